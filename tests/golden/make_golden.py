@@ -1,0 +1,147 @@
+"""Generate the golden fixtures in this directory by running jaxrwkv's own
+``inner_loop`` source.
+
+    python tests/golden/make_golden.py --reference-src <jaxrwkv checkout>/src
+
+JAX cannot be installed in the build image, so the reference modules
+(src/jaxrwkv/rwkv{4,5,5_2,6,7}.py and llm.py, loaded unmodified from the
+checkout) are executed against ``tests/golden/jax_standin`` — a NumPy
+implementation of the handful of jax calls those functions make.  The package
+``__init__`` of jaxrwkv (tokenizers, HuggingFace hub) is bypassed by registering
+an empty package object and importing the version modules directly.
+
+For every case the Base, Scan and AssociativeScan classes are all run in
+float64 on float32-representable inputs; the Base and AssociativeScan results
+are stored (Scan is asserted equal to Base and only its max deviation is
+recorded).  Inputs are stored as float32, outputs as float64.
+"""
+import argparse
+import importlib
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+
+
+def load_reference(src):
+    sys.path.insert(0, os.path.join(HERE, "jax_standin"))
+    pkg = types.ModuleType("jaxrwkv")
+    pkg.__path__ = [os.path.join(src, "jaxrwkv")]
+    sys.modules["jaxrwkv"] = pkg
+    return {v: importlib.import_module(f"jaxrwkv.rwkv{v}") for v in ("4", "5", "5_2", "6", "7")}
+
+
+def f64(d, names):
+    return [np.asarray(d[n], dtype=np.float64) for n in names]
+
+
+def run_v7(mod, d):
+    import jax.numpy as jnp
+    out = {}
+    B = d["r"].shape[0]
+    for cls in ("BaseRWKV", "ScanRWKV", "AssociativeScanRWKV"):
+        ss, ys = [], []
+        for i in range(B):
+            args = [jnp.asarray(x[i]) for x in f64(d, ["r", "w", "k", "v", "a", "b", "s0"])]
+            s, y = getattr(mod, cls).inner_loop(*args, int(d["length"][i]), jnp.asarray(d["new_starts"][i]))
+            ss.append(np.asarray(s)); ys.append(np.asarray(y))
+        out[cls] = (np.stack(ss), np.stack(ys))
+    return out
+
+
+def run_v6(mod, d, version):
+    import jax.numpy as jnp
+    out = {}
+    B = d["r"].shape[0]
+    for cls in ("BaseRWKV", "ScanRWKV", "AssociativeScanRWKV"):
+        ss, ys = [], []
+        for i in range(B):
+            r, k, v, s0 = [jnp.asarray(x[i]) for x in f64(d, ["r", "k", "v", "s0"])]
+            w = np.asarray(d["w"], dtype=np.float64)
+            w = jnp.asarray(w[i] if version == "6" else w)
+            u = jnp.asarray(np.asarray(d["u"], dtype=np.float64))
+            s, y = getattr(mod, cls).inner_loop(r, k, v, w, u, s0, int(d["length"][i]),
+                                                jnp.asarray(d["new_starts"][i]))
+            ss.append(np.asarray(s)); ys.append(np.asarray(y))
+        out[cls] = (np.stack(ss), np.stack(ys))
+    return out
+
+
+def run_v4(mod, d):
+    import jax.numpy as jnp
+    out = {}
+    B = d["r"].shape[0]
+    for cls in ("BaseRWKV", "ScanRWKV", "AssociativeScanRWKV"):
+        ss, ys = [], []
+        for i in range(B):
+            r, k, v, s0 = [jnp.asarray(x[i]) for x in f64(d, ["r", "k", "v", "s0"])]
+            w, u = [jnp.asarray(x) for x in f64(d, ["w", "u"])]
+            s, y = getattr(mod, cls).inner_loop(r, k, v, w, u, s0, int(d["length"][i]),
+                                                jnp.asarray(d["new_starts"][i]))
+            ss.append(np.asarray(s)); ys.append(np.asarray(y))
+        out[cls] = (np.stack(ss), np.stack(ys))
+    return out
+
+
+def save(name, d, res):
+    base_s, base_y = res["BaseRWKV"]
+    scan_s, scan_y = res["ScanRWKV"]
+    dev = max(np.abs(scan_s - base_s).max(), np.abs(scan_y - base_y).max())
+    assert dev < 1e-9, (name, dev)
+    arrays = {f"in_{k}": v for k, v in d.items()}
+    arrays.update(base_s=base_s, base_y=base_y, assoc_s=res["AssociativeScanRWKV"][0],
+                  assoc_y=res["AssociativeScanRWKV"][1], scan_vs_base_maxdev=np.float64(dev))
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **arrays)
+    print(f"{name}: scan-vs-base {dev:.2e}, {os.path.getsize(path) / 1024:.0f} KiB")
+
+
+def set_starts(d, starts, lengths):
+    ns = np.zeros_like(d["new_starts"])
+    for i, row in enumerate(starts):
+        ns[i, list(row)] = True
+    d["new_starts"] = ns
+    d["length"] = np.asarray(lengths, dtype=np.uint32)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference-src", required=True, help="path to the jaxrwkv checkout's src/ directory")
+    a = ap.parse_args()
+    mods = load_reference(a.reference_src)
+    sys.path.insert(0, ROOT)
+    from oracle.inputs import make_wkv7_inputs, make_wkv6_inputs, make_wkv4_inputs
+
+    # RWKV-7 -----------------------------------------------------------------------------
+    d = make_wkv7_inputs(2, 40, 2, 64, seed=101)                      # config-1 style: start at t=0 only
+    save("v7_plain", d, run_v7(mods["7"], d))
+    d = make_wkv7_inputs(3, 48, 1, 64, seed=102, s0_scale=0.5)
+    # row 0: carried state (no start at 0), adjacent starts, length lands on a start (state quirk)
+    # row 1: start at 0 and mid-sequence, length mid-chunk; row 2: length == 0
+    set_starts(d, [(17, 18, 30), (0, 16, 33), (5,)], [30, 41, 0])
+    save("v7_resets", d, run_v7(mods["7"], d))
+    d = make_wkv7_inputs(2, 21, 3, 8, seed=103, s0_scale=1.0)         # small head size, oracle-only
+    set_starts(d, [(0, 7), (3, 20)], [21, 13])
+    save("v7_small", d, run_v7(mods["7"], d))
+
+    # RWKV-6 / 5.2 / 5 -------------------------------------------------------------------
+    for version, seed in (("6", 201), ("5_2", 202), ("5", 203)):
+        d = make_wkv6_inputs(2, 40, 2, 64, seed=seed, s0_scale=0.5, version=version)
+        set_starts(d, [(11, 12, 25), (0,)], [25, 33])
+        save(f"v{version}_resets", d, run_v6(mods[version], d, version))
+
+    # RWKV-4 -----------------------------------------------------------------------------
+    d = make_wkv4_inputs(2, 40, 128, seed=301, default_state=True)
+    set_starts(d, [(0,), (9, 10, 31)], [40, 31])
+    save("v4_default_state", d, run_v4(mods["4"], d))
+    d = make_wkv4_inputs(2, 33, 128, seed=302, default_state=False)
+    set_starts(d, [(), (20,)], [0, 27])
+    save("v4_carried_state", d, run_v4(mods["4"], d))
+
+
+if __name__ == "__main__":
+    main()
