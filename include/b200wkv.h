@@ -1,0 +1,93 @@
+/*
+ * b200wkv — C ABI of the B200 (sm_100a) WKV state-recurrence kernels.
+ *
+ * This is the boundary a host framework binds: plain pointers and sizes, no
+ * C++ or framework types.  Every pointer named "device" must be valid on the
+ * CUDA device that is current when the call is made; `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  Calls only
+ * enqueue work on `stream`: they never allocate, free, synchronise or retain
+ * caller memory, and they return 0 on success or a negative B200WKV_E* code
+ * (text via b200wkv_strerror) without having launched anything.
+ *
+ * Tensor layouts are the ones jaxrwkv's batched custom calls use (C order):
+ *   r, w, k, v, a, b, y, d*   (B, T, H, N)   element type = `dtype`
+ *   states                    (B, H, N, N)   element type = `dtype`
+ *   length                    (B,)           uint32
+ *   new_starts                (B, T)         one byte per flag (0 / non-zero)
+ * N (the head size) must be 64.
+ */
+#ifndef B200WKV_H_
+#define B200WKV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define B200WKV_F32  0
+#define B200WKV_BF16 1
+
+/* status codes */
+#define B200WKV_OK            0
+#define B200WKV_EDTYPE       -1   /* dtype is not B200WKV_F32 / B200WKV_BF16            */
+#define B200WKV_ESHAPE       -2   /* a dimension is < 1, N != 64, or a size overflows   */
+#define B200WKV_ENULL        -3   /* a required pointer is NULL                          */
+#define B200WKV_ERESIDUAL    -4   /* residual buffer smaller than *_residual_bytes()     */
+#define B200WKV_ELAUNCH      -5   /* the CUDA runtime refused the launch                 */
+#define B200WKV_EUNSUPPORTED -6   /* combination not available in this build             */
+#define B200WKV_ESCRATCH     -7   /* problem larger than a fixed built-in scratch area   */
+
+/* flags (bit set) */
+#define B200WKV_FLAG_SEQUENTIAL 1u   /* force the token-sequential CUDA-core kernels     */
+
+const char* b200wkv_strerror(int status);
+/* ABI version of the loaded library (incremented on incompatible change). */
+int b200wkv_abi_version(void);
+
+/* ---------------------------------------------------------------- RWKV-7 ----
+ * Replaces the XLA custom calls "wkv7-fwd-{fp32,bf16}" / "wkv7-bwd-{fp32,bf16}"
+ * that jaxrwkv binds at src/jaxrwkv/rwkv7.py:372-375 and :406-408 (handlers
+ * WKV7FwdF32/WKV7FwdBF16/WKV7BwdF32/WKV7BwdBF16 registered at :461-465).
+ * Operand order follows those calls: (w, r, k, v, a, b, s, length, new_starts).
+ * `w` is the raw log-log decay: the kernel applies exp(-exp(w)) itself, as
+ * BaseRWKV.inner_loop does at rwkv7.py:201.
+ *
+ * Semantics are those of BaseRWKV.inner_loop (rwkv7.py:199-220): a start flag
+ * zeroes the state before its token, s_out is the state after token length-1
+ * (the input state when length == 0; length > T is treated as T), and the
+ * state is carried in fp32 inside the kernel.
+ *
+ * `residual` is an opaque device buffer the forward fills for the backward
+ * (the counterpart of the reference's s_restore/sa_restore results,
+ * rwkv7.py:363-364).  Pass NULL/0 for inference: nothing is saved then.
+ */
+size_t b200wkv7_residual_bytes(int dtype, int B, int T, int H, int N);
+
+int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N,
+                 const void* w, const void* r, const void* k, const void* v,
+                 const void* a, const void* b, const void* s0,
+                 const uint32_t* length, const uint8_t* new_starts,
+                 void* y, void* s_out,
+                 void* residual, size_t residual_bytes, unsigned flags);
+
+/* Backward: cotangents dy (B,T,H,N) and ds_out (B,H,N,N) in, gradients of all six
+ * streams and of the initial state out (the reference's result order is
+ * gw, gr, gk, gv, ga, gb, gs — rwkv7.py:406).  dy or ds_out may be NULL (= zeros).
+ * Unlike the reference kernels (README "CudaRWKV" caveats), gradients flow from
+ * s_out and into s0, and start flags cut the dependency exactly. */
+int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N,
+                 const void* w, const void* r, const void* k, const void* v,
+                 const void* a, const void* b, const void* s0,
+                 const uint32_t* length, const uint8_t* new_starts,
+                 const void* dy, const void* ds_out,
+                 const void* residual, size_t residual_bytes,
+                 void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
+                 unsigned flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* B200WKV_H_ */

@@ -1,0 +1,201 @@
+"""GPU parity tests of the RWKV-7 kernels, called through the C ABI (ctypes) via the
+host operator, against the CPU oracle and the committed reference fixtures."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from jaxrwkv_b200 import rwkv7, _lib
+from conftest import rel_err
+from gpu_util import NAMES7, TOL, to_dev, rounded, flags, npf, wkv7_case
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def run_fwd(t, length, ns, flags_=0):
+    B = t["k"].shape[0]
+    (s, y), res = rwkv7.batched_wkv7_fwd(t["r"], t["w"], t["k"], t["v"], t["a"], t["b"], t["s0"], length, ns, B, flags=flags_)
+    return s, y, res
+
+
+def check_fwd(d, dtype, flags_=0, tol=None):
+    t = to_dev(d, dtype)
+    length, ns = flags(d)
+    s, y, _ = run_fwd(t, length, ns, flags_)
+    so, yo = oracle.wkv7_base_batched(*rounded(t), d["length"], d["new_starts"])
+    tol = tol or TOL[dtype]
+    assert rel_err(npf(y), yo) < tol, ("y", rel_err(npf(y), yo))
+    for i in range(so.shape[0]):     # per sequence: a zero state must come back as exact zeros
+        e = rel_err(npf(s[i]), so[i])
+        assert e < tol, ("s_out", i, e)
+    return s, y
+
+
+def check_bwd(d, dtype, seed=0, use_gy=True, use_gs=True, flags_=0):
+    t = to_dev(d, dtype)
+    length, ns = flags(d)
+    B = t["k"].shape[0]
+    s, y, res = run_fwd(t, length, ns, flags_)
+    g = torch.Generator().manual_seed(seed)
+    gy = torch.randn(y.shape, generator=g).to(dtype).cuda() if use_gy else None
+    gs = torch.randn(s.shape, generator=g).to(dtype).cuda() if use_gs else None
+    got = rwkv7.batched_wkv7_bwd(res, (gs, gy), B, flags=flags_)
+    ref = oracle.wkv7_bwd_batched(*rounded(t), d["length"], d["new_starts"],
+                                  npf(gy) if use_gy else np.zeros(y.shape), npf(gs) if use_gs else np.zeros(s.shape))
+    for n, a, b in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), got, ref):
+        e = rel_err(npf(a), b)
+        assert e < TOL[dtype], (n, e)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["v7_plain", "v7_resets"])
+def test_fwd_reference_fixtures(golden, case, dtype):
+    """Against the outputs of jaxrwkv's own Base and AssociativeScan inner_loop."""
+    g = golden(case)
+    d = {n: g["in_" + n] for n in NAMES7 + ("length", "new_starts")}
+    t = to_dev(d, dtype)
+    length, ns = flags(d)
+    s, y, _ = run_fwd(t, length, ns)
+    tol = TOL[dtype] if dtype == torch.float32 else 3e-2   # fixtures were computed on unrounded inputs
+    assert rel_err(npf(y), g["base_y"]) < tol
+    for i in range(s.shape[0]):
+        assert rel_err(npf(s[i]), g["base_s"][i]) < tol
+        ym, sd = oracle.quirk_mask(d["new_starts"][i], int(d["length"][i]))
+        # AssociativeScanRWKV, excluding the positions its index shift forces to zero
+        assert rel_err(npf(y[i])[~ym], g["assoc_y"][i][~ym]) < tol
+        if not sd:
+            assert rel_err(npf(s[i]), g["assoc_s"][i]) < tol
+
+
+def test_fwd_config1_fp32():
+    """B=2, T=256, H=4, N=64, start only at t=0, zero initial state, length=T."""
+    check_fwd(wkv7_case(2, 256, 4, seed=1234), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [1, 2, 15, 16, 17, 31, 64, 65, 130])
+def test_fwd_ragged_lengths_and_starts(T, dtype):
+    rng = np.random.default_rng(T)
+    starts = [sorted(set(rng.integers(0, T, size=3).tolist())), [0] + ([T - 1] if T > 1 else []), [], [min(1, T - 1)]]
+    lengths = [T, max(T - 1, 0), 0, T + 5]
+    check_fwd(wkv7_case(4, T, 2, seed=100 + T, s0_scale=0.5, starts=starts, lengths=lengths), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_fwd_adjacent_starts_every_position(dtype):
+    T = 40
+    d = wkv7_case(2, T, 1, seed=5, s0_scale=1.0, starts=[range(T), [7, 8, 9, 24, 25]], lengths=[T, 9])
+    check_fwd(d, dtype)
+
+
+def test_fwd_config2_shape_bf16():
+    """B=8, T=1024, H=12 with Bernoulli(1/256) starts and lengths uniform in [T/2, T]."""
+    d = wkv7_case(8, 1024, 12, seed=1235, p_start=1 / 256, random_length=True)
+    check_fwd(d, torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [1, 7, 8, 9, 16, 17, 24, 33, 70])
+def test_bwd_ragged(T, dtype):
+    rng = np.random.default_rng(T)
+    starts = [sorted(set(rng.integers(0, T, size=2).tolist())), [0], [T // 2, min(T // 2 + 1, T - 1)]]
+    lengths = [T, max(T - 3, 0), 0]
+    check_bwd(wkv7_case(3, T, 2, seed=200 + T, s0_scale=0.5, starts=starts, lengths=lengths), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bwd_missing_cotangents(dtype):
+    d = wkv7_case(2, 40, 2, seed=9, s0_scale=0.5, starts=[[0, 20], [3]], lengths=[33, 40])
+    check_bwd(d, dtype, use_gy=True, use_gs=False)
+    check_bwd(d, dtype, use_gy=False, use_gs=True)
+
+
+def test_bwd_training_shape_bf16():
+    check_bwd(wkv7_case(2, 512, 4, seed=11, p_start=1 / 128, random_length=True, s0_scale=0.1), torch.bfloat16)
+
+
+def test_bwd_config1_fp32():
+    check_bwd(wkv7_case(2, 256, 4, seed=1234), torch.float32)
+
+
+def test_operator_autograd_and_vmap_on_gpu():
+    """CudaRWKV.inner_loop end to end: vmap over batch, gradients for all inputs and the state."""
+    d = wkv7_case(3, 48, 2, seed=21, s0_scale=0.5, p_start=0.05, random_length=True)
+    t = to_dev(d, torch.float32)
+    length, ns = flags(d)
+    leaves = [t[n].clone().requires_grad_(True) for n in NAMES7]
+    s, y = torch.vmap(rwkv7.CudaRWKV.inner_loop)(*leaves, length.cuda(), ns.cuda())
+    gy, gs = torch.randn_like(y), torch.randn_like(s)
+    ((y * gy).sum() + (s * gs).sum()).backward()
+    ref = oracle.wkv7_bwd_batched(*rounded(t), d["length"], d["new_starts"], npf(gy), npf(gs))
+    for n, leaf, g in zip(NAMES7, leaves, ref):
+        assert rel_err(npf(leaf.grad), g) < 1e-4, n
+    # a replicated batch gives identical rows (tests/vmap_test.py of jaxrwkv)
+    rep = [x[:1].expand(3, *x.shape[1:]).contiguous() for x in (t[n] for n in NAMES7)]
+    s2, y2 = torch.vmap(rwkv7.CudaRWKV.inner_loop, in_dims=(0,) * 7 + (None, None))(*rep, length[0].cuda(), ns[0].cuda())
+    assert torch.equal(y2[0], y2[1]) and torch.equal(y2[0], y2[2]) and torch.equal(s2[0], s2[2])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_run_to_run_determinism(dtype):
+    d = wkv7_case(2, 100, 2, seed=31, p_start=0.05, s0_scale=0.3)
+    t = to_dev(d, dtype)
+    length, ns = flags(d)
+    outs = []
+    for _ in range(2):
+        s, y, res = run_fwd(t, length, ns)
+        g = rwkv7.batched_wkv7_bwd(res, (s.clone(), y.clone()), 2)
+        outs.append((s, y) + tuple(g))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+def test_full_size_properties_bf16():
+    """Headline shape B=8, T=4096, H=32, bf16.  Size-independent properties instead of an
+    oracle run: (1) a start flag at t splits the sequence into independent parts, so the
+    tail equals a separate call on the tail; (2) y and s_out are linear in (v, s0), and
+    scaling by 2 is exact in binary floating point, so the results must be bit-identical
+    up to that factor; (3) the carried state composes: one call == two calls of half length."""
+    B, T, H = 8, 4096, 32
+    d = wkv7_case(B, T, H, seed=1237, s0_scale=0.1)
+    d["new_starts"][:, 0] = False
+    d["new_starts"][:, 1500] = True
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    s, y, _ = run_fwd(t, length, ns)
+    assert torch.isfinite(y.float()).all() and torch.isfinite(s.float()).all()
+    # (1) tail after the start flag == fresh call on the tail with any initial state
+    tail = {n: t[n][:, 1500:].contiguous() for n in NAMES7[:-1]}
+    tail["s0"] = torch.randn_like(t["s0"])
+    ns_tail = ns[:, 1500:].contiguous()
+    s_t, y_t, _ = run_fwd(tail, torch.full((B,), T - 1500), ns_tail)
+    assert torch.equal(y_t, y[:, 1500:]) and torch.equal(s_t, s)
+    # (2) exact homogeneity in (v, s0)
+    t2 = dict(t); t2["v"] = t["v"] * 2; t2["s0"] = t["s0"] * 2
+    s2, y2, _ = run_fwd(t2, length, ns)
+    assert torch.equal(y2, y * 2) and torch.equal(s2, s * 2)
+    # (3) state carry across calls, in fp32 so that the hand-over is not rounded
+    B3, H3 = 2, 4
+    d3 = wkv7_case(B3, T, H3, seed=1238, s0_scale=0.1)
+    t3 = to_dev(d3, torch.float32)
+    l3, ns3 = flags(d3)
+    s_full, y_full, _ = run_fwd(t3, l3, ns3)
+    half = T // 2
+    first = {n: t3[n][:, :half].contiguous() for n in NAMES7[:-1]}; first["s0"] = t3["s0"]
+    s_a, y_a, _ = run_fwd(first, torch.full((B3,), half), ns3[:, :half].contiguous())
+    second = {n: t3[n][:, half:].contiguous() for n in NAMES7[:-1]}; second["s0"] = s_a
+    s_b, y_b, _ = run_fwd(second, torch.full((B3,), half), ns3[:, half:].contiguous())
+    assert torch.equal(torch.cat([y_a, y_b], 1), y_full) and torch.equal(s_b, s_full)
+
+
+def test_calls_fail_loudly_on_bad_input():
+    d = wkv7_case(1, 16, 1, seed=1)
+    t = to_dev(d, torch.float32)
+    length, ns = flags(d)
+    bad = dict(t); bad["w"] = t["w"].to(torch.bfloat16)
+    with pytest.raises(_lib.B200WKVError):
+        run_fwd(bad, length, ns)
+    cpu = {n: x.cpu() for n, x in t.items()}
+    with pytest.raises(_lib.B200WKVError, match="no CPU path"):
+        run_fwd(cpu, length, ns)
