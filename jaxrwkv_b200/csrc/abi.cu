@@ -11,6 +11,12 @@ int wkv7_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w,
                  const uint8_t* ns, const void* dy, const void* ds_out, const void* residual, void* dw, void* dr,
                  void* dk, void* dv, void* da, void* db, void* ds0);
 
+size_t wkv7_chunk_residual_bytes(int B, int T, int H);
+int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
+                   const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+                   void* s_out, void* residual, void* dbg);
+int wkv7_chunk_status();
+
 static int check_dims(int dtype, int B, int T, int H, int N) {
     if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
     if (B < 1 || T < 1 || H < 1 || N != kN) return B200WKV_ESHAPE;
@@ -53,7 +59,11 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void
     if (st != B200WKV_OK) return st;
     if (!w || !r || !k || !v || !a || !b || !s0 || !length || !new_starts || !y || !s_out) return B200WKV_ENULL;
     if (residual != nullptr && residual_bytes < b200wkv7_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
-    (void)flags;
+    // bf16 inference runs on the tensor-core kernel; training keeps the sequential pair until the
+    // chunked backward consumes the 64-token checkpoints
+    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL) && residual == nullptr)
+        return wkv7_chunk_fwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
+                              nullptr, nullptr);
     return wkv7_seq_fwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
                         residual);
 }

@@ -1,0 +1,489 @@
+// RWKV-7 WKV forward, chunked along T on the Blackwell tensor cores (bf16 I/O, fp32 state).
+//
+// One CTA (128 threads) per (batch, head) walks the sequence in chunks of up to 64 tokens.  With
+// L_t = prod_{s<=t} decay_s (per key channel, inside the chunk) and the scaled operands
+//   A~_t = a_t * L_{t-1}   R~_t = r_t * L_t   B~_t = b_t / L_t   K~_t = k_t / L_t
+//   B^_t = b_t * L_C / L_t K^_t = k_t * L_C / L_t                (L_C = decay over the whole chunk)
+// the recurrence  S <- S diag(decay) + (S a) b^T + v k^T,  y = S r  becomes, for a chunk entered
+// with state S0 (row = value index, column = key index):
+//   [A_ab A_ak; P_rb P_rk] = [A~; R~] [B~; K~]^T            strictly / inclusively lower triangular
+//   G   = A_ak V + A~ S0^T                                  (token x value)
+//   sa  = (I - A_ab)^-1 G                                   row t is S_{t-1} a_t
+//   Y   = P_rk V + R~ S0^T + P_rb sa
+//   S_C = S0 diag(L_C) + sa^T B^ + V^T K^
+// All products are tcgen05.mma (M=128, bf16 operands from shared memory, fp32 accumulators in
+// TMEM); the unit-triangular inverse is an fp32 forward substitution on CUDA cores; the state
+// stays in TMEM in fp32 for the whole sequence.  Start flags and `length` never need masks:
+// a chunk simply ends early in front of a start position and at `length`, and the rows of a
+// short chunk are zero-filled.
+//
+// Semantics: BaseRWKV.inner_loop of jaxrwkv (src/jaxrwkv/rwkv7.py:199-220).
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace b200wkv {
+
+namespace {
+
+constexpr int kC = 64;                 // tokens per full chunk == checkpoint spacing
+constexpr int CB64 = 1040;             // column-block pitch of a 64-row operand slab (64*16 + 16 pad)
+constexpr int CB128 = 2064;            // ... of a 128-row slab
+constexpr int SLAB64 = 8 * CB64;       // 8320
+constexpr int SLAB128 = 8 * CB128;     // 16512
+constexpr int LF_PITCH = 68;           // floats per row of the fp32 triangular matrix
+constexpr float kCumFloor = -60.f;     // floor of the in-chunk cumulative log-decay (keeps 1/L finite)
+
+// shared-memory map (bytes)
+constexpr int OFF_AR = 0;                        // [A~ ; R~]           128-row slab   (LF aliases AR+BK)
+constexpr int OFF_BK = OFF_AR + SLAB128;         // [B~ ; K~]           128-row slab
+constexpr int OFF_BH = OFF_BK + SLAB128;         // B^                  64-row slab
+constexpr int OFF_KH = OFF_BH + SLAB64;          // K^                  64-row slab
+constexpr int OFF_SA = OFF_KH + SLAB64;          // sa                  64-row slab   } consecutive: the MN-major
+constexpr int OFF_V = OFF_SA + SLAB64;           // V                   64-row slab   } A operands of the state
+constexpr int OFF_M2A = OFF_V + SLAB64;          // [A_ak ; P_rk]       128-row slab  } update span two slabs
+constexpr int OFF_G = OFF_M2A;                   // G (aliases M2A once the A_ak/P_rk product is done)
+constexpr int OFF_TP = OFF_M2A + SLAB128;        // [Tinv ; P_rb]       128-row slab   (CUM aliases TP)
+constexpr int OFF_S0 = OFF_TP + SLAB128;         // S0 in bf16          64-row slab
+constexpr int OFF_SMALL = OFF_S0 + SLAB64;
+constexpr int OFF_LF = OFF_AR;
+constexpr int OFF_CUM = OFF_TP;
+struct Small {
+    float h1[kN];        // cumulative log-decay of tokens 0..31
+    float tot[kN];       // ... of the whole chunk
+    float lam[kN];       // exp(tot)
+    uint64_t bar[4];
+    uint32_t nsm[2];
+    uint32_t tmem;
+};
+constexpr int SMEM_BYTES = OFF_SMALL + (int)sizeof(Small);
+static_assert(LF_PITCH * 64 * 4 <= 2 * SLAB128, "triangular matrix must fit over AR+BK");
+static_assert(64 * 64 * 4 <= SLAB128, "cumulative-sum buffer must fit over TP");
+
+__device__ int g_status;  // last device-side error (0 = none); see wkv7_chunk_status()
+
+__device__ __forceinline__ uint32_t pack2(float x, float y) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+}
+__device__ __forceinline__ void unpack8(uint4 raw, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+// 16-byte store of row `row`, column block `cblk` of a slab
+__device__ __forceinline__ void slab_store(unsigned char* slab, int cb, int row, int cblk, uint4 val) {
+    *reinterpret_cast<uint4*>(slab + cblk * cb + row * 16) = val;
+}
+
+__global__ void __launch_bounds__(128, 2)
+wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ r,
+                      const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                      const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                      const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
+                      const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
+                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ dbg) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
+    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int L = min((int)length[bi], Tlen);
+    const size_t tok_stride = (size_t)H * kN;
+    const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
+    const size_t st_row = ((size_t)bh * kN + (tid & 63)) * kN;  // this thread's state row (threads 0..63)
+    const int nBlk = (Tlen + kC - 1) / kC;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tc::mbar_init(&sm.bar[i], 1);
+        tc::mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(&sm.tmem, 256);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tbase = sm.tmem;
+    const uint32_t lane_addr = tbase + ((uint32_t)(warp * 32) << 16);  // this warp's 32 TMEM lanes
+    const uint32_t D1 = 0, D2 = 128, DS = 192;                        // TMEM column offsets (D3 aliases D1)
+    bool failed = false;
+
+    // ---- state into TMEM (rows 0..63 = S0 in fp32, rows 64..127 are never read) --------------
+    {
+        float s[64];
+        if (tid < 64) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) unpack8(*reinterpret_cast<const uint4*>(s0 + st_row + c * 8), &s[c * 8]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 64; ++c) s[c] = 0.f;
+        }
+        tc::tmem_st32(lane_addr + DS, s);
+        tc::tmem_st32(lane_addr + DS + 32, s + 32);
+        tc::tmem_wait_st();
+    }
+
+    const uint32_t sAR = tc::smem_u32(smem + OFF_AR), sBK = tc::smem_u32(smem + OFF_BK);
+    const uint32_t sBH = tc::smem_u32(smem + OFF_BH), sKH = tc::smem_u32(smem + OFF_KH);
+    const uint32_t sSA = tc::smem_u32(smem + OFF_SA), sV = tc::smem_u32(smem + OFF_V);
+    const uint32_t sM2A = tc::smem_u32(smem + OFF_M2A), sG = tc::smem_u32(smem + OFF_G);
+    const uint32_t sTP = tc::smem_u32(smem + OFF_TP), sS0 = tc::smem_u32(smem + OFF_S0);
+    constexpr uint32_t ID_128x128_KK = tc::make_idesc(128, 128, false, false);
+    constexpr uint32_t ID_128x64_KK = tc::make_idesc(128, 64, false, false);
+    constexpr uint32_t ID_128x64_KM = tc::make_idesc(128, 64, false, true);
+    constexpr uint32_t ID_128x64_MM = tc::make_idesc(128, 64, true, true);
+
+    float* cum = reinterpret_cast<float*>(smem + OFF_CUM);  // [64][64]
+    float* lf = reinterpret_cast<float*>(smem + OFF_LF);    // [64][LF_PITCH]
+    const int tsub = tid >> 3, jb = tid & 7;                // staging unit: tokens 16q+tsub, channels 8jb..8jb+7
+
+    int p = 0;
+    uint32_t par = 0;
+    while (true) {
+        // ================= boundary at position p: TMEM holds the state after token p-1 =================
+        const bool want_out = (p == L);
+        const bool want_ck = (ckpt != nullptr) && (p % kC == 0) && (p < Tlen);
+        if (tid < 64 && (want_out || want_ck)) {
+            float s[64];
+            tc::tmem_ld32(lane_addr + DS, s);
+            tc::tmem_ld32(lane_addr + DS + 32, s + 32);
+            tc::tmem_wait_ld();
+            if (want_out) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(s_out + st_row + c * 8) = pack8(&s[c * 8]);
+            }
+            if (want_ck) {
+                float* dst = ckpt + (((size_t)bh * nBlk + p / kC) * kN + tid) * kN;
+#pragma unroll
+                for (int c = 0; c < 16; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+            }
+        }
+        if (p >= Tlen) break;
+
+        // ================= extent of this chunk =================
+        const int be = min(((p >> 6) + 1) << 6, Tlen);
+        if (tid < 64) {
+            const int pos = p + tid;
+            const bool f = (pos < be) && (new_starts[(size_t)bi * Tlen + pos] != 0);
+            const uint32_t m = __ballot_sync(0xffffffffu, f);
+            if (lane == 0) sm.nsm[warp] = m;
+        }
+        // ================= stage inputs (registers) =================
+        uint4 raw[4][5];   // r, k, v, a, b
+        float lw[4][8];    // log-decay  -exp(w)
+        __syncthreads();   // nsm visible; previous chunk's shared-memory readers are done
+        const uint64_t mask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
+        const bool reset_here = (mask & 1ull) != 0;
+        int p1 = be;
+        if ((mask >> 1) != 0) p1 = p + __ffsll((long long)(mask >> 1));
+        if (L > p && L < p1) p1 = L;
+        const int n = p1 - p;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int t = q * 16 + tsub;
+            if (t < n) {
+                const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
+                float wf[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(w + g)), wf);
+                raw[q][0] = __ldg(reinterpret_cast<const uint4*>(r + g));
+                raw[q][1] = __ldg(reinterpret_cast<const uint4*>(k + g));
+                raw[q][2] = __ldg(reinterpret_cast<const uint4*>(v + g));
+                raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
+                raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) lw[q][e] = -__expf(wf[e]);
+            } else {
+#pragma unroll
+                for (int m = 0; m < 5; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) lw[q][e] = 0.f;
+            }
+            *reinterpret_cast<float4*>(&cum[t * 64 + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
+            *reinterpret_cast<float4*>(&cum[t * 64 + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
+        }
+        __syncthreads();
+        {   // inclusive scan over tokens, two independent halves of 32 per channel
+            const int j = tid & 63, half = tid >> 6;
+            float run = 0.f;
+#pragma unroll 8
+            for (int tt = 0; tt < 32; ++tt) {
+                const int t = half * 32 + tt;
+                run += cum[t * 64 + j];
+                cum[t * 64 + j] = run;
+            }
+            if (half == 0) sm.h1[j] = run;
+            else sm.tot[j] = run;   // second-half sum for now
+        }
+        __syncthreads();
+        if (tid < 64) {
+            const float t2 = fmaxf(sm.h1[tid] + sm.tot[tid], kCumFloor);
+            sm.tot[tid] = t2;
+            sm.lam[tid] = __expf(t2);
+        }
+        __syncthreads();
+        // ================= scaled operands into the slabs =================
+        {
+            float h1v[8], totv[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { h1v[e] = sm.h1[jb * 8 + e]; totv[e] = sm.tot[jb * 8 + e]; }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int t = q * 16 + tsub;
+                float c[8];
+                *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * 64 + jb * 8]);
+                *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * 64 + jb * 8 + 4]);
+                float rf[8], kf[8], af[8], bf[8], o[8];
+                unpack8(raw[q][0], rf); unpack8(raw[q][1], kf); unpack8(raw[q][3], af); unpack8(raw[q][4], bf);
+                float eL[8], eI[8], eP[8], eE[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float cc = fmaxf(c[e] + (q >= 2 ? h1v[e] : 0.f), kCumFloor);
+                    const float cp = fmaxf(cc - lw[q][e], kCumFloor);   // cumulative log-decay before this token
+                    eL[e] = __expf(cc); eI[e] = __expf(-cc); eP[e] = __expf(fminf(cp, 0.f)); eE[e] = __expf(totv[e] - cc);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = af[e] * eP[e];
+                slab_store(smem + OFF_AR, CB128, t, jb, pack8(o));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = rf[e] * eL[e];
+                slab_store(smem + OFF_AR, CB128, 64 + t, jb, pack8(o));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = bf[e] * eI[e];
+                slab_store(smem + OFF_BK, CB128, t, jb, pack8(o));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = kf[e] * eI[e];
+                slab_store(smem + OFF_BK, CB128, 64 + t, jb, pack8(o));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = bf[e] * eE[e];
+                slab_store(smem + OFF_BH, CB64, t, jb, pack8(o));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = kf[e] * eE[e];
+                slab_store(smem + OFF_KH, CB64, t, jb, pack8(o));
+                slab_store(smem + OFF_V, CB64, t, jb, raw[q][2]);
+            }
+        }
+        // ================= entering state: bf16 copy for the products, decayed fp32 copy back to TMEM =====
+        if (tid < 64) {
+            float s[64];
+            if (reset_here) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) s[c] = 0.f;
+            } else {
+                tc::tmem_ld32(lane_addr + DS, s);
+                tc::tmem_ld32(lane_addr + DS + 32, s + 32);
+                tc::tmem_wait_ld();
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_S0, CB64, tid, c, pack8(&s[c * 8]));
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 l4 = *reinterpret_cast<const float4*>(&sm.lam[c * 4]);
+                s[c * 4] *= l4.x; s[c * 4 + 1] *= l4.y; s[c * 4 + 2] *= l4.z; s[c * 4 + 3] *= l4.w;
+            }
+            tc::tmem_st32(lane_addr + DS, s);
+            tc::tmem_st32(lane_addr + DS + 32, s + 32);
+            tc::tmem_wait_st();
+        }
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        // ================= M1: pairwise products and the S0 products =================
+        if (tid == 0) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + D1, tc::make_desc(sAR + ks * 2 * CB128, CB128, 128),
+                        tc::make_desc(sBK + ks * 2 * CB128, CB128, 128), ID_128x128_KK, ks > 0);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + D2, tc::make_desc(sAR + ks * 2 * CB128, CB128, 128),
+                        tc::make_desc(sS0 + ks * 2 * CB64, CB64, 128), ID_128x64_KK, ks > 0);
+            tc::commit(&sm.bar[0]);
+        }
+        if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
+        tc::fence_after_sync();
+        // ================= E1: triangular masks, operands of the next products =================
+        {
+            const int t = tid & 63;
+            float d[64];
+            // columns 0..63: A_ab (rows 0..63) / P_rb (rows 64..127)
+            tc::tmem_ld32(lane_addr + D1, d);
+            tc::tmem_ld32(lane_addr + D1 + 32, d + 32);
+            tc::tmem_wait_ld();
+            if (tid < 64) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    *reinterpret_cast<float4*>(&lf[t * LF_PITCH + c * 4]) =
+                        make_float4(c * 4 + 0 < t ? d[c * 4 + 0] : 0.f, c * 4 + 1 < t ? d[c * 4 + 1] : 0.f,
+                                    c * 4 + 2 < t ? d[c * 4 + 2] : 0.f, c * 4 + 3 < t ? d[c * 4 + 3] : 0.f);
+            } else {
+#pragma unroll
+                for (int s = 0; s < 64; ++s) d[s] = (s <= t) ? d[s] : 0.f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) slab_store(smem + OFF_TP, CB128, 64 + t, c, pack8(&d[c * 8]));
+            }
+            // columns 64..127: A_ak (rows 0..63, strict) / P_rk (rows 64..127, inclusive)
+            tc::tmem_ld32(lane_addr + D1 + 64, d);
+            tc::tmem_ld32(lane_addr + D1 + 96, d + 32);
+            tc::tmem_wait_ld();
+            const int lim = (tid < 64) ? t : t + 1;   // keep columns s < lim
+#pragma unroll
+            for (int s = 0; s < 64; ++s) d[s] = (s < lim) ? d[s] : 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_M2A, CB128, tid, c, pack8(&d[c * 8]));
+        }
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        // ================= M2: G += A_ak V, Ypart += P_rk V ; meanwhile the triangular inverse =================
+        if (tid == 0) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + D2, tc::make_desc(sM2A + ks * 2 * CB128, CB128, 128),
+                        tc::make_desc(sV + ks * 256, 128, CB64), ID_128x64_KM, true);
+            tc::commit(&sm.bar[1]);
+        }
+        if (tid >= 64) {
+            // column c of X = (I - A_ab)^-1 by forward substitution over the rows
+            const int c = tid - 64;
+            float x[64];
+#pragma unroll
+            for (int t = 0; t < 64; ++t) x[t] = 0.f;
+#pragma unroll
+            for (int t = 0; t < 64; ++t) {
+                float a0 = (t == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int m4 = 0; m4 < (t + 3) / 4; ++m4) {
+                    const float4 l = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + m4 * 4]);
+                    a0 = fmaf(l.x, x[m4 * 4 + 0], a0); a1 = fmaf(l.y, x[m4 * 4 + 1], a1);
+                    a2 = fmaf(l.z, x[m4 * 4 + 2], a2); a3 = fmaf(l.w, x[m4 * 4 + 3], a3);
+                }
+                x[t] = (a0 + a1) + (a2 + a3);
+            }
+            unsigned char* col = smem + OFF_TP + (c >> 3) * CB128 + (c & 7) * 2;
+#pragma unroll
+            for (int t = 0; t < 64; ++t) *reinterpret_cast<__nv_bfloat16*>(col + t * 16) = __float2bfloat16_rn(x[t]);
+            if (dbg != nullptr && bh == 0 && p == 0) {
+#pragma unroll
+                for (int t = 0; t < 64; ++t) dbg[4096 + t * 64 + c] = x[t];
+            }
+        } else {
+            if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
+            tc::fence_after_sync();
+            float g[64];
+            tc::tmem_ld32(lane_addr + D2, g);
+            tc::tmem_ld32(lane_addr + D2 + 32, g + 32);
+            tc::tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_G, CB64, tid, c, pack8(&g[c * 8]));
+            if (dbg != nullptr && bh == 0 && p == 0) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) { dbg[2 * 4096 + tid * 64 + c] = g[c]; dbg[tid * 64 + c] = lf[tid * LF_PITCH + c]; }
+            }
+        }
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        // ================= M3: sa = Tinv G =================
+        if (tid == 0) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + D1, tc::make_desc(sTP + ks * 2 * CB128, CB128, 128),
+                        tc::make_desc(sG + ks * 256, 128, CB64), ID_128x64_KM, ks > 0);
+            tc::commit(&sm.bar[2]);
+        }
+        if (tid < 64) {
+            if (!tc::mbar_wait(&sm.bar[2], par)) failed = true;
+            tc::fence_after_sync();
+            float sa[64];
+            tc::tmem_ld32(lane_addr + D1, sa);
+            tc::tmem_ld32(lane_addr + D1 + 32, sa + 32);
+            tc::tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_SA, CB64, tid, c, pack8(&sa[c * 8]));
+            if (dbg != nullptr && bh == 0 && p == 0) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) dbg[3 * 4096 + tid * 64 + c] = sa[c];
+            }
+        }
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        // ================= M4: Y += P_rb sa ; S += sa^T B^ + V^T K^ =================
+        if (tid == 0) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + D2, tc::make_desc(sTP + ks * 2 * CB128, CB128, 128),
+                        tc::make_desc(sSA + ks * 256, 128, CB64), ID_128x64_KM, true);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + DS, tc::make_desc(sSA + ks * 256, 128, CB64),
+                        tc::make_desc(sBH + ks * 256, 128, CB64), ID_128x64_MM, true);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma(tbase + DS, tc::make_desc(sV + ks * 256, 128, CB64),
+                        tc::make_desc(sKH + ks * 256, 128, CB64), ID_128x64_MM, true);
+            tc::commit(&sm.bar[3]);
+        }
+        if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
+        tc::fence_after_sync();
+        if (tid >= 64) {
+            const int t = tid - 64;
+            float yv[64];
+            tc::tmem_ld32(lane_addr + D2, yv);
+            tc::tmem_ld32(lane_addr + D2 + 32, yv + 32);
+            tc::tmem_wait_ld();
+            if (t < n) {
+                __nv_bfloat16* dst = y + seq_base + (size_t)(p + t) * tok_stride;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&yv[c * 8]);
+            }
+            if (dbg != nullptr && bh == 0 && p == 0) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) dbg[4 * 4096 + t * 64 + c] = yv[c];
+            }
+        }
+        tc::fence_before_sync();
+        p = p1;
+        par ^= 1u;
+    }
+    if (failed) atomicExch(&g_status, 1);
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tbase, 256);
+}
+
+}  // namespace
+
+size_t wkv7_chunk_residual_bytes(int B, int T, int H) {
+    return (size_t)B * H * ((T + kC - 1) / kC) * kN * kN * sizeof(float);
+}
+
+int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
+                   const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+                   void* s_out, void* residual, void* dbg) {
+    typedef __nv_bfloat16 bf;
+    if (cudaFuncSetAttribute(wkv7_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        return B200WKV_ELAUNCH;
+    wkv7_chunk_fwd_kernel<<<B * H, 128, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
+                                                          (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
+                                                          (bf*)y, (bf*)s_out, (float*)residual, (float*)dbg);
+    return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+}
+
+// Reads and clears the device-side error word (synchronises the device; diagnostics only).
+int wkv7_chunk_status() {
+    int h = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&h, g_status, sizeof(int)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return h;
+}
+
+}  // namespace b200wkv

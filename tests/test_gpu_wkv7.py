@@ -199,3 +199,90 @@ def test_calls_fail_loudly_on_bad_input():
     cpu = {n: x.cpu() for n, x in t.items()}
     with pytest.raises(_lib.B200WKVError, match="no CPU path"):
         run_fwd(cpu, length, ns)
+
+
+# ---------------------------------------------------------------- tensor-core (chunked) forward
+def run_fwd_infer(t, length, ns):
+    """bf16 forward without a residual: dispatches to the chunked tcgen05 kernel."""
+    B = t["k"].shape[0]
+    (s, y), _ = rwkv7.batched_wkv7_fwd(t["r"], t["w"], t["k"], t["v"], t["a"], t["b"], t["s0"], length, ns, B,
+                                       need_residual=False)
+    return s, y
+
+
+def check_fwd_chunk(d, tol=TOL[torch.bfloat16]):
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    s, y = run_fwd_infer(t, length, ns)
+    so, yo = oracle.wkv7_base_batched(*rounded(t), d["length"], d["new_starts"])
+    ey = rel_err(npf(y), yo)
+    assert ey < tol, ("y", ey)
+    for i in range(so.shape[0]):
+        e = rel_err(npf(s[i]), so[i])
+        assert e < tol, ("s_out", i, e)
+    # and against the sequential fp32-arithmetic kernel on the same bf16 inputs
+    s2, y2, _ = run_fwd(t, length, ns, _lib.FLAG_SEQUENTIAL)
+    assert rel_err(npf(y), npf(y2)) < tol
+
+
+def test_chunk_fwd_single_full_chunk():
+    check_fwd_chunk(wkv7_case(1, 64, 1, seed=41))
+
+
+def test_chunk_fwd_carried_state_multi_chunk():
+    check_fwd_chunk(wkv7_case(2, 256, 2, seed=42, s0_scale=0.5, starts=[[], [0]], lengths=[256, 256]))
+
+
+@pytest.mark.parametrize("T", [1, 2, 15, 16, 17, 63, 65, 130, 200])
+def test_chunk_fwd_ragged_lengths_and_starts(T):
+    rng = np.random.default_rng(T)
+    starts = [sorted(set(rng.integers(0, T, size=3).tolist())), [0] + ([T - 1] if T > 1 else []), [], [min(1, T - 1)]]
+    lengths = [T, max(T - 1, 0), 0, T + 5]
+    check_fwd_chunk(wkv7_case(4, T, 2, seed=300 + T, s0_scale=0.5, starts=starts, lengths=lengths))
+
+
+def test_chunk_fwd_adjacent_starts_every_position():
+    T = 70
+    check_fwd_chunk(wkv7_case(2, T, 1, seed=45, s0_scale=1.0, starts=[range(T), [7, 8, 9, 24, 25, 64, 65]], lengths=[T, 9]))
+
+
+def test_chunk_fwd_config2_shape():
+    check_fwd_chunk(wkv7_case(8, 1024, 12, seed=1235, p_start=1 / 256, random_length=True))
+
+
+def test_chunk_fwd_reference_fixtures(golden):
+    for case in ("v7_plain", "v7_resets"):
+        g = golden(case)
+        d = {n: g["in_" + n] for n in NAMES7 + ("length", "new_starts")}
+        t = to_dev(d, torch.bfloat16)
+        length, ns = flags(d)
+        s, y = run_fwd_infer(t, length, ns)
+        assert rel_err(npf(y), g["base_y"]) < 3e-2       # fixtures were computed on unrounded inputs
+        for i in range(s.shape[0]):
+            assert rel_err(npf(s[i]), g["base_s"][i]) < 3e-2
+
+
+def test_chunk_fwd_full_size_properties():
+    """Headline shape on the tensor-core kernel: finite, deterministic, exactly homogeneous in
+    (v, s0) under scaling by 2, and start flags / state hand-over agree with separate calls to
+    within the bf16 tolerance (chunk boundaries differ between the two runs, so not bit-equal)."""
+    B, T, H = 8, 4096, 32
+    d = wkv7_case(B, T, H, seed=1237, s0_scale=0.1)
+    d["new_starts"][:, 0] = False
+    d["new_starts"][:, 1500] = True
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    s, y = run_fwd_infer(t, length, ns)
+    s_again, y_again = run_fwd_infer(t, length, ns)
+    assert torch.isfinite(y.float()).all() and torch.isfinite(s.float()).all()
+    assert torch.equal(y, y_again) and torch.equal(s, s_again)
+    t2 = dict(t); t2["v"] = t["v"] * 2; t2["s0"] = t["s0"] * 2
+    s2, y2 = run_fwd_infer(t2, length, ns)
+    assert torch.equal(y2, y * 2) and torch.equal(s2, s * 2)
+    tail = {n: t[n][:, 1500:].contiguous() for n in NAMES7[:-1]}
+    tail["s0"] = torch.randn_like(t["s0"])
+    s_t, y_t = run_fwd_infer(tail, torch.full((B,), T - 1500), ns[:, 1500:].contiguous())
+    assert rel_err(npf(y_t), npf(y[:, 1500:])) < 1e-2 and rel_err(npf(s_t), npf(s)) < 1e-2
+    # sequential kernel on the same inputs
+    s_q, y_q, _ = run_fwd(t, length, ns, _lib.FLAG_SEQUENTIAL)
+    assert rel_err(npf(y), npf(y_q)) < TOL[torch.bfloat16] and rel_err(npf(s), npf(s_q)) < TOL[torch.bfloat16]
