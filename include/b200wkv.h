@@ -62,7 +62,9 @@ int b200wkv_abi_version(void);
  *
  * `residual` is an opaque device buffer the forward fills for the backward
  * (the counterpart of the reference's s_restore/sa_restore results,
- * rwkv7.py:363-364).  Pass NULL/0 for inference: nothing is saved then.
+ * rwkv7.py:363-364).  Pass NULL/0 for inference: nothing is saved then.  The
+ * backward must be called with the same dtype and flags as the forward that
+ * filled the buffer.
  */
 size_t b200wkv7_residual_bytes(int dtype, int B, int T, int H, int N);
 

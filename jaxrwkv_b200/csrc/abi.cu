@@ -15,6 +15,10 @@ size_t wkv7_chunk_residual_bytes(int B, int T, int H);
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
                    void* s_out, void* residual, void* dbg);
+int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
+                   const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
+                   const void* ds_out, const void* residual, void* dw, void* dr, void* dk, void* dv, void* da,
+                   void* db, void* ds0);
 int wkv7_chunk_status();
 
 static int check_dims(int dtype, int B, int T, int H, int N) {
@@ -48,7 +52,12 @@ int b200wkv_abi_version(void) { return 1; }
 
 size_t b200wkv7_residual_bytes(int dtype, int B, int T, int H, int N) {
     if (check_dims(dtype, B, T, H, N) != B200WKV_OK) return 0;
-    return wkv7_seq_residual_bytes(B, T, H);
+    // fp32 uses the sequential kernels (a state every 16 tokens); bf16 uses the chunked tensor-core
+    // kernels (a state every 64 tokens) unless B200WKV_FLAG_SEQUENTIAL asks otherwise, so size for both
+    const size_t seq = wkv7_seq_residual_bytes(B, T, H);
+    if (dtype == B200WKV_F32) return seq;
+    const size_t chk = wkv7_chunk_residual_bytes(B, T, H);
+    return seq > chk ? seq : chk;
 }
 
 int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void* w, const void* r, const void* k,
@@ -59,11 +68,9 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void
     if (st != B200WKV_OK) return st;
     if (!w || !r || !k || !v || !a || !b || !s0 || !length || !new_starts || !y || !s_out) return B200WKV_ENULL;
     if (residual != nullptr && residual_bytes < b200wkv7_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
-    // bf16 inference runs on the tensor-core kernel; training keeps the sequential pair until the
-    // chunked backward consumes the 64-token checkpoints
-    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL) && residual == nullptr)
+    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL))
         return wkv7_chunk_fwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
-                              nullptr, nullptr);
+                              residual, nullptr);
     return wkv7_seq_fwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
                         residual);
 }
@@ -79,7 +86,10 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void
         !da || !db || !ds0)
         return B200WKV_ENULL;
     if (residual_bytes < b200wkv7_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
-    (void)flags;
+    // must match the kernel family that filled the residual in b200wkv7_fwd (same dtype and flags)
+    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL))
+        return wkv7_chunk_bwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, length, new_starts, dy, ds_out,
+                              residual, dw, dr, dk, dv, da, db, ds0);
     return wkv7_seq_bwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, dy, ds_out,
                         residual, dw, dr, dk, dv, da, db, ds0);
 }

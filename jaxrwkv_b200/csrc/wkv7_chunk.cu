@@ -20,18 +20,12 @@
 // Semantics: BaseRWKV.inner_loop of jaxrwkv (src/jaxrwkv/rwkv7.py:199-220).
 #include "common.cuh"
 #include "tc05.cuh"
+#include "chunk_common.cuh"
 
 namespace b200wkv {
 
 namespace {
 
-constexpr int kC = 64;                 // tokens per full chunk == checkpoint spacing
-constexpr int CB64 = 1040;             // column-block pitch of a 64-row operand slab (64*16 + 16 pad)
-constexpr int CB128 = 2064;            // ... of a 128-row slab
-constexpr int SLAB64 = 8 * CB64;       // 8320
-constexpr int SLAB128 = 8 * CB128;     // 16512
-constexpr int LF_PITCH = 68;           // floats per row of the fp32 triangular matrix
-constexpr float kCumFloor = -60.f;     // floor of the in-chunk cumulative log-decay (keeps 1/L finite)
 
 // shared-memory map (bytes)
 constexpr int OFF_AR = 0;                        // [A~ ; R~]           128-row slab   (LF aliases AR+BK)
@@ -61,33 +55,14 @@ static_assert(64 * 64 * 4 <= SLAB128, "cumulative-sum buffer must fit over TP");
 
 __device__ int g_status;  // last device-side error (0 = none); see wkv7_chunk_status()
 
-__device__ __forceinline__ uint32_t pack2(float x, float y) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ uint4 pack8(const float* f) {
-    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
-}
-__device__ __forceinline__ void unpack8(uint4 raw, float* f) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float2 t = __bfloat1622float2(h[i]);
-        f[2 * i] = t.x; f[2 * i + 1] = t.y;
-    }
-}
-// 16-byte store of row `row`, column block `cblk` of a slab
-__device__ __forceinline__ void slab_store(unsigned char* slab, int cb, int row, int cblk, uint4 val) {
-    *reinterpret_cast<uint4*>(slab + cblk * cb + row * 16) = val;
-}
-
 __global__ void __launch_bounds__(128, 2)
 wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ r,
                       const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                       const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
-                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ dbg) {
+                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
+                      float* __restrict__ dbg) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -155,6 +130,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             if (want_out) {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(s_out + st_row + c * 8) = pack8(&s[c * 8]);
+                if (s_at_len != nullptr) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        *reinterpret_cast<float4*>(s_at_len + st_row + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+                }
             }
             if (want_ck) {
                 float* dst = ckpt + (((size_t)bh * nBlk + p / kC) * kN + tid) * kN;
@@ -462,9 +442,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
 }  // namespace
 
-size_t wkv7_chunk_residual_bytes(int B, int T, int H) {
-    return (size_t)B * H * ((T + kC - 1) / kC) * kN * kN * sizeof(float);
-}
+size_t wkv7_chunk_residual_bytes(int B, int T, int H) { return chunk_residual_floats(B, T, H) * sizeof(float); }
 
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
@@ -474,8 +452,16 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
         return B200WKV_ELAUNCH;
     wkv7_chunk_fwd_kernel<<<B * H, 128, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
-                                                          (bf*)y, (bf*)s_out, (float*)residual, (float*)dbg);
+                                                          (bf*)y, (bf*)s_out, (float*)residual,
+                                                          residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
+                                                          (float*)dbg);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+}
+
+int* wkv7_chunk_status_word() {
+    int* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_status) != cudaSuccess) return nullptr;
+    return ptr;
 }
 
 // Reads and clears the device-side error word (synchronises the device; diagnostics only).

@@ -1,0 +1,615 @@
+// RWKV-7 WKV backward, chunked along T on the Blackwell tensor cores (bf16 I/O, fp32 carries).
+//
+// One CTA (256 threads) per (batch, head) walks the chunks of the forward in reverse.  A chunk is
+// re-entered from the forward's saved state S0 and recomputed (scaled operands, the four
+// triangular Gram blocks, T = (I - A_ab)^-1, sa), then with dS = gradient of the state leaving
+// the chunk, L = in-chunk cumulative decay (L_C at the chunk end) and dSL = dS diag(L_C):
+//   dsa   = T^T (B~ dSL^T + P_rb^T dY)                           row t is dS_t b_t
+//   dV    = K~ dSL^T + P_rk^T dY + A_ak^T dsa
+//   W     = [V; sa] [dY; dsa]^T                                  upper-triangular Gram blocks
+//   dK~'  = W_v,dsa A~ + W_v,dy R~ + V  dSL      dk = dK~' / L_t
+//   dB~'  = W_sa,dsa A~ + W_sa,dy R~ + sa dSL    db = dB~' / L_t
+//   dR~'  = dY  S0 + W_sa,dy^T B~ + W_v,dy^T K~  dr = dR~' * L_t
+//   dA~'  = dsa S0 + W_sa,dsa^T B~ + W_v,dsa^T K~  da = dA~' * L_{t-1}
+//   dS0   = dSL + dsa^T A~ + dY^T R~                             carried to the previous chunk
+// The decay gradient uses D_t = sum_i dS_t[i,:] S_t[i,:]:  with u_t = r dr - b db - k dk + a da the
+// recurrence D_{t-1} = D_t + u_t holds, d(log decay)_t = D_{t-1} - a_t da_t, and D is re-anchored
+// exactly at every chunk start from dS0 and S0, so rounding never accumulates across chunks.
+// All products are tcgen05.mma (M=128, bf16 operands in shared memory, fp32 accumulators in TMEM).
+//
+// Semantics: reverse-mode derivative of BaseRWKV.inner_loop of jaxrwkv (src/jaxrwkv/rwkv7.py:199-220).
+#include "common.cuh"
+#include "tc05.cuh"
+#include "chunk_common.cuh"
+
+namespace b200wkv {
+
+namespace {
+
+// shared-memory map (bytes); one CTA per SM
+constexpr int OFF_AR = 0;                         // [A~ ; R~]          128-row slab
+constexpr int OFF_BK = OFF_AR + SLAB128;          // [B~ ; K~]          128-row slab
+constexpr int OFF_VSA = OFF_BK + SLAB128;         // [V ; sa]           128-row slab
+constexpr int OFF_DD = OFF_VSA + SLAB128;         // [dY ; dsa]         128-row slab
+constexpr int OFF_S0 = OFF_DD + SLAB128;          // S0 bf16 [i][j]     64-row slab
+constexpr int OFF_DSL = OFF_S0 + SLAB64;          // dS diag(L_C) bf16  64-row slab
+constexpr int OFF_TINV = OFF_DSL + SLAB64;        // T                  64-row slab  } adjacent
+constexpr int OFF_AAK = OFF_TINV + SLAB64;        // A_ak               64-row slab  }
+constexpr int OFF_X = OFF_AAK + SLAB64;           // P_rb | P_rk | G | Gd  (4 x 64-row slabs), later W
+constexpr int OFF_PRB = OFF_X;
+constexpr int OFF_PRK = OFF_PRB + SLAB64;
+constexpr int OFF_G = OFF_PRK + SLAB64;
+constexpr int OFF_GD = OFF_G + SLAB64;
+constexpr int OFF_WY = OFF_X;                     // [V ; sa] . dY^T    128-row slab  } adjacent, alias X
+constexpr int OFF_WSA = OFF_WY + SLAB128;         // [V ; sa] . dsa^T   128-row slab  }
+constexpr int OFF_LF = OFF_X + 4 * SLAB64;        // fp32 A_ab for the inverse; later the decay-gradient scan
+constexpr int OFF_CUM = OFF_LF + LF_PITCH * 64 * 4;   // fp32 cumulative log-decay [64][LF_PITCH]
+constexpr int OFF_DSF = OFF_CUM + LF_PITCH * 64 * 4;   // fp32 dS carried across chunks [64][LF_PITCH]
+constexpr int OFF_SMALL = OFF_DSF + LF_PITCH * 64 * 4;
+static_assert(2 * SLAB128 <= 4 * SLAB64, "W must fit over the X region");
+struct Small {
+    float h1[kN];
+    float tot[kN];
+    float lam[kN];
+    float d_in[kN];        // D carried from the chunk processed before (later in time)
+    float d_part[2][kN];   // partial column sums of the new anchor
+    uint64_t bar[5];
+    uint32_t nsm[2];
+    uint32_t tmem;
+};
+constexpr int SMEM_BYTES = OFF_SMALL + (int)sizeof(Small);
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+// TMEM columns
+constexpr uint32_t T_D1 = 0;      // 128: Gram blocks of the forward recompute, later W
+constexpr uint32_t T_G = 128;     // 64 : G, later [dR~' ; dA~']
+constexpr uint32_t T_GD = 192;    // 64 : [Gd ; dV]
+constexpr uint32_t T_SA = 256;    // 64 : sa
+constexpr uint32_t T_DSA = 320;   // 64 : dsa
+constexpr uint32_t T_TMP = 384;   // 64 : dsa^T A~ + dY^T R~
+constexpr uint32_t T_KB = 448;    // 64 : [dK~' ; dB~']
+
+struct Op { uint32_t addr, step, lbo, sbo; };   // operand walk: descriptor of K-step ks starts at addr + ks*step
+__device__ __forceinline__ Op kmaj128(uint32_t a) { return {a, 2 * CB128, CB128, 128}; }
+__device__ __forceinline__ Op kmaj64(uint32_t a) { return {a, 2 * CB64, CB64, 128}; }
+__device__ __forceinline__ Op mnmaj128(uint32_t a) { return {a, 256, 128, CB128}; }
+__device__ __forceinline__ Op mnmaj64(uint32_t a) { return {a, 256, 128, CB64}; }
+// four K=16 steps (64 deep) of D (+)= A B
+__device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, bool accumulate) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+        tc::mma(d, tc::make_desc(a.addr + ks * a.step, a.lbo, a.sbo), tc::make_desc(b.addr + ks * b.step, b.lbo, b.sbo),
+                idesc, accumulate || ks > 0);
+}
+
+__global__ void __launch_bounds__(256, 1)
+wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ r,
+                      const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                      const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                      const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
+                      const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ ds_out,
+                      const float* __restrict__ ckpt, const float* __restrict__ s_at_len,
+                      __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ dr, __nv_bfloat16* __restrict__ dk,
+                      __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
+                      __nv_bfloat16* __restrict__ ds0, int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
+    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hsel = warp >> 2;     // TMEM lane quadrant / column half handled by this warp
+    const int row = quad * 32 + lane;                // TMEM lane == tile row
+    const int L = min((int)length[bi], Tlen);
+    const size_t tok_stride = (size_t)H * kN;
+    const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
+    const size_t st_base = (size_t)bh * kN * kN;
+    const int nBlk = (Tlen + kC - 1) / kC;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 5; ++i) tc::mbar_init(&sm.bar[i], 1);
+        tc::mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(&sm.tmem, 512);
+    float* dsf = reinterpret_cast<float*>(smem + OFF_DSF);   // [64][LF_PITCH]
+    float* cum = reinterpret_cast<float*>(smem + OFF_CUM);   // [64][LF_PITCH]
+    float* lf = reinterpret_cast<float*>(smem + OFF_LF);     // [64][LF_PITCH]
+    for (int idx = tid; idx < 64 * LF_PITCH; idx += 256) dsf[idx] = 0.f;
+    if (tid < 64) sm.d_in[tid] = 0.f;
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tbase = sm.tmem;
+    const uint32_t lane_addr = tbase + ((uint32_t)(quad * 32) << 16);
+    bool failed = false;
+
+    const uint32_t sAR = tc::smem_u32(smem + OFF_AR), sBK = tc::smem_u32(smem + OFF_BK);
+    const uint32_t sVSA = tc::smem_u32(smem + OFF_VSA), sDD = tc::smem_u32(smem + OFF_DD);
+    const uint32_t sS0 = tc::smem_u32(smem + OFF_S0), sDSL = tc::smem_u32(smem + OFF_DSL);
+    const uint32_t sTINV = tc::smem_u32(smem + OFF_TINV), sAAK = tc::smem_u32(smem + OFF_AAK);
+    const uint32_t sPRB = tc::smem_u32(smem + OFF_PRB), sG = tc::smem_u32(smem + OFF_G), sGD = tc::smem_u32(smem + OFF_GD);
+    const uint32_t sWY = tc::smem_u32(smem + OFF_WY), sWSA = tc::smem_u32(smem + OFF_WSA);
+    constexpr uint32_t ID_N128_KK = tc::make_idesc(128, 128, false, false);
+    constexpr uint32_t ID_KK = tc::make_idesc(128, 64, false, false);
+    constexpr uint32_t ID_KM = tc::make_idesc(128, 64, false, true);
+    constexpr uint32_t ID_MM = tc::make_idesc(128, 64, true, true);
+    constexpr uint32_t HALF = 64 * 16;   // byte offset of row 64 inside a 128-row slab column block
+
+    const int tsub = tid >> 3, jb = tid & 7;   // staging unit: tokens 32q + tsub (q = 0,1), channels 8jb..8jb+7
+    const int si = tid & 63, scq = tid >> 6;   // state element ownership: row si, columns 16scq..16scq+15
+    uint32_t par = 0;
+
+    for (int blk = nBlk - 1; blk >= 0; --blk) {
+        const int bs = blk * kC, be = min(bs + kC, Tlen);
+        // chunk starts inside this block: its first token, every start flag, and `length`
+        __syncthreads();
+        if (tid < 64) {
+            const int pos = bs + tid;
+            const bool f = (pos < be) && (tid == 0 || new_starts[(size_t)bi * Tlen + pos] != 0 || pos == L);
+            const uint32_t m = __ballot_sync(0xffffffffu, f);
+            if (lane == 0) sm.nsm[warp] = m;
+        }
+        __syncthreads();
+        const uint64_t cmask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
+        int p1 = be;
+        while (p1 > bs) {
+            const int rel = p1 - bs;   // 1..64
+            const uint64_t below = (rel >= 64) ? cmask : (cmask & ((1ull << rel) - 1ull));
+            const int p = bs + 63 - __clzll((long long)below);
+            const int n = p1 - p;
+            const bool reset_here = new_starts[(size_t)bi * Tlen + p] != 0;
+            // ---------------- cotangent of the returned state enters at position `length` ----------------
+            if (p1 == L && ds_out != nullptr) {
+                float g[16];
+                unpack8(*reinterpret_cast<const uint4*>(ds_out + st_base + si * kN + scq * 16), g);
+                unpack8(*reinterpret_cast<const uint4*>(ds_out + st_base + si * kN + scq * 16 + 8), g + 8);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) dsf[si * LF_PITCH + scq * 16 + e] += g[e];
+                if (tid < 64) {
+                    float acc = 0.f;
+                    for (int i = 0; i < 64; ++i)
+                        acc += __bfloat162float(ds_out[st_base + i * kN + tid]) * s_at_len[st_base + i * kN + tid];
+                    sm.d_in[tid] += acc;
+                }
+            }
+            // ---------------- stage the chunk: inputs, cumulative decay ----------------
+            uint4 raw[2][6];   // r, k, v, a, b, dy
+            float lw[2][8];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int t = q * 32 + tsub;
+                if (t < n) {
+                    const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
+                    float wf[8];
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(w + g)), wf);
+                    raw[q][0] = __ldg(reinterpret_cast<const uint4*>(r + g));
+                    raw[q][1] = __ldg(reinterpret_cast<const uint4*>(k + g));
+                    raw[q][2] = __ldg(reinterpret_cast<const uint4*>(v + g));
+                    raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
+                    raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
+                    raw[q][5] = (dy != nullptr) ? __ldg(reinterpret_cast<const uint4*>(dy + g)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) lw[q][e] = -__expf(wf[e]);
+                } else {
+#pragma unroll
+                    for (int m = 0; m < 6; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) lw[q][e] = 0.f;
+                }
+                *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
+                *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
+            }
+            __syncthreads();
+            if (tid < 128) {
+                const int j = tid & 63, half = tid >> 6;
+                float run = 0.f;
+#pragma unroll 8
+                for (int tt = 0; tt < 32; ++tt) {
+                    const int t = half * 32 + tt;
+                    run += cum[t * LF_PITCH + j];
+                    cum[t * LF_PITCH + j] = run;
+                }
+                if (half == 0) sm.h1[j] = run;
+                else sm.tot[j] = run;
+            }
+            __syncthreads();
+            if (tid < 64) {
+                const float t2 = fmaxf(sm.h1[tid] + sm.tot[tid], kCumFloor);
+                sm.tot[tid] = t2;
+                sm.lam[tid] = __expf(t2);
+            }
+            __syncthreads();
+            {
+                float h1v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h1v[e] = sm.h1[jb * 8 + e];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int t = q * 32 + tsub;
+                    float c[8];
+                    *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8]);
+                    *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8 + 4]);
+                    float rf[8], kf[8], af[8], bf[8], o[8];
+                    unpack8(raw[q][0], rf); unpack8(raw[q][1], kf); unpack8(raw[q][3], af); unpack8(raw[q][4], bf);
+                    float eL[8], eI[8], eP[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float cc = fmaxf(c[e] + (q == 1 ? h1v[e] : 0.f), kCumFloor);
+                        const float cp = fminf(fmaxf(cc - lw[q][e], kCumFloor), 0.f);
+                        eL[e] = __expf(cc); eI[e] = __expf(-cc); eP[e] = __expf(cp);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = af[e] * eP[e];
+                    slab_store(smem + OFF_AR, CB128, t, jb, pack8(o));
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = rf[e] * eL[e];
+                    slab_store(smem + OFF_AR, CB128, 64 + t, jb, pack8(o));
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = bf[e] * eI[e];
+                    slab_store(smem + OFF_BK, CB128, t, jb, pack8(o));
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = kf[e] * eI[e];
+                    slab_store(smem + OFF_BK, CB128, 64 + t, jb, pack8(o));
+                    slab_store(smem + OFF_VSA, CB128, t, jb, raw[q][2]);
+                    slab_store(smem + OFF_DD, CB128, t, jb, raw[q][5]);
+                }
+            }
+            // ---------------- entering state (bf16) and decayed incoming state gradient (bf16) ----------------
+            const float* s0src = reset_here ? nullptr : ((p % kC == 0) ? ckpt + ((size_t)bh * nBlk + p / kC) * kN * kN
+                                                                        : s_at_len + st_base);
+            {
+                float s[16], g[16];
+                if (s0src != nullptr) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const float4 x = *reinterpret_cast<const float4*>(s0src + si * kN + scq * 16 + c4 * 4);
+                        s[c4 * 4] = x.x; s[c4 * 4 + 1] = x.y; s[c4 * 4 + 2] = x.z; s[c4 * 4 + 3] = x.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) s[e] = 0.f;
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) g[e] = dsf[si * LF_PITCH + scq * 16 + e] * sm.lam[scq * 16 + e];
+                slab_store(smem + OFF_S0, CB64, si, scq * 2, pack8(s));
+                slab_store(smem + OFF_S0, CB64, si, scq * 2 + 1, pack8(s + 8));
+                slab_store(smem + OFF_DSL, CB64, si, scq * 2, pack8(g));
+                slab_store(smem + OFF_DSL, CB64, si, scq * 2 + 1, pack8(g + 8));
+            }
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            // ================= R1: Gram blocks, A~ S0^T =================
+            if (tid == 0) {
+                tc::fence_after_sync();
+                mma_k64(tbase + T_D1, kmaj128(sAR), kmaj128(sBK), ID_N128_KK, false);
+                mma_k64(tbase + T_G, kmaj128(sAR), kmaj64(sS0), ID_KK, false);
+                tc::commit(&sm.bar[0]);
+            }
+            if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
+            tc::fence_after_sync();
+            {
+                const int t = row & 63;
+                float d[64];
+                tc::tmem_ld32(lane_addr + T_D1 + hsel * 64, d);
+                tc::tmem_ld32(lane_addr + T_D1 + hsel * 64 + 32, d + 32);
+                tc::tmem_wait_ld();
+                if (row < 64 && hsel == 0) {          // A_ab, strictly lower, fp32 for the inverse
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        *reinterpret_cast<float4*>(&lf[t * LF_PITCH + c * 4]) =
+                            make_float4(c * 4 + 0 < t ? d[c * 4 + 0] : 0.f, c * 4 + 1 < t ? d[c * 4 + 1] : 0.f,
+                                        c * 4 + 2 < t ? d[c * 4 + 2] : 0.f, c * 4 + 3 < t ? d[c * 4 + 3] : 0.f);
+                } else {
+                    const int lim = (row < 64) ? t : t + 1;   // A_ak strict; P_rb, P_rk inclusive
+#pragma unroll
+                    for (int s = 0; s < 64; ++s) d[s] = (s < lim) ? d[s] : 0.f;
+                    unsigned char* dst = smem + ((row < 64) ? OFF_AAK : (hsel == 0 ? OFF_PRB : OFF_PRK));
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) slab_store(dst, CB64, t, c, pack8(&d[c * 8]));
+                }
+            }
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            // ================= R2: G += A_ak V ; [Gd ; dVpart] = [B~;K~] dSL^T + [P_rb|P_rk]^T dY ; inverse =================
+            if (tid == 0) {
+                tc::fence_after_sync();
+                mma_k64(tbase + T_G, kmaj64(sAAK), mnmaj128(sVSA), ID_KM, true);
+                mma_k64(tbase + T_GD, kmaj128(sBK), kmaj64(sDSL), ID_KK, false);
+                mma_k64(tbase + T_GD, mnmaj64(sPRB), mnmaj128(sDD), ID_MM, true);
+                tc::commit(&sm.bar[1]);
+            }
+            if (warp == 2 || warp == 3) {
+                const int c = tid - 64;
+                float x[64];
+#pragma unroll
+                for (int t = 0; t < 64; ++t) x[t] = 0.f;
+#pragma unroll
+                for (int t = 0; t < 64; ++t) {
+                    float a0 = (t == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                    for (int m4 = 0; m4 < (t + 3) / 4; ++m4) {
+                        const float4 l = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + m4 * 4]);
+                        a0 = fmaf(l.x, x[m4 * 4 + 0], a0); a1 = fmaf(l.y, x[m4 * 4 + 1], a1);
+                        a2 = fmaf(l.z, x[m4 * 4 + 2], a2); a3 = fmaf(l.w, x[m4 * 4 + 3], a3);
+                    }
+                    x[t] = (a0 + a1) + (a2 + a3);
+                }
+                unsigned char* col = smem + OFF_TINV + (c >> 3) * CB64 + (c & 7) * 2;
+#pragma unroll
+                for (int t = 0; t < 64; ++t) *reinterpret_cast<__nv_bfloat16*>(col + t * 16) = __float2bfloat16_rn(x[t]);
+            } else if (quad < 2) {
+                if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
+                tc::fence_after_sync();
+                float g[32], gd[32];
+                tc::tmem_ld32(lane_addr + T_G + hsel * 32, g);
+                tc::tmem_ld32(lane_addr + T_GD + hsel * 32, gd);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    slab_store(smem + OFF_G, CB64, row, hsel * 4 + c, pack8(&g[c * 8]));
+                    slab_store(smem + OFF_GD, CB64, row, hsel * 4 + c, pack8(&gd[c * 8]));
+                }
+            }
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            // ================= R3: sa = T G ; dsa = T^T Gd =================
+            if (tid == 0) {
+                tc::fence_after_sync();
+                mma_k64(tbase + T_SA, kmaj64(sTINV), mnmaj64(sG), ID_KM, false);
+                mma_k64(tbase + T_DSA, mnmaj64(sTINV), mnmaj64(sGD), ID_MM, false);
+                tc::commit(&sm.bar[2]);
+            }
+            if (quad < 2) {
+                if (!tc::mbar_wait(&sm.bar[2], par)) failed = true;
+                tc::fence_after_sync();
+                float x[32], z[32];
+                tc::tmem_ld32(lane_addr + T_SA + hsel * 32, x);
+                tc::tmem_ld32(lane_addr + T_DSA + hsel * 32, z);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    slab_store(smem + OFF_VSA, CB128, 64 + row, hsel * 4 + c, pack8(&x[c * 8]));
+                    slab_store(smem + OFF_DD, CB128, 64 + row, hsel * 4 + c, pack8(&z[c * 8]));
+                }
+            }
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            // ================= R4: dV += A_ak^T dsa ; W = [V;sa][dY;dsa]^T ; tmp = dY^T R~ + dsa^T A~ =================
+            if (tid == 0) {
+                tc::fence_after_sync();
+                mma_k64(tbase + T_GD, mnmaj64(sTINV), mnmaj128(sDD + HALF), ID_MM, true);
+                mma_k64(tbase + T_D1, kmaj128(sVSA), kmaj128(sDD), ID_N128_KK, false);
+                mma_k64(tbase + T_TMP, mnmaj128(sDD), mnmaj128(sAR + HALF), ID_MM, false);
+                mma_k64(tbase + T_TMP, mnmaj128(sDD + HALF), mnmaj128(sAR), ID_MM, true);
+                tc::commit(&sm.bar[3]);
+            }
+            if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
+            tc::fence_after_sync();
+            {
+                const int t = row & 63;
+                float d[64];
+                tc::tmem_ld32(lane_addr + T_D1 + hsel * 64, d);
+                tc::tmem_ld32(lane_addr + T_D1 + hsel * 64 + 32, d + 32);
+                tc::tmem_wait_ld();
+                const int lo = t + hsel;   // keep s >= t for the dY blocks, s > t for the dsa blocks
+#pragma unroll
+                for (int s = 0; s < 64; ++s) d[s] = (s >= lo) ? d[s] : 0.f;
+                unsigned char* dst = smem + (hsel == 0 ? OFF_WY : OFF_WSA);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) slab_store(dst, CB128, row, c, pack8(&d[c * 8]));
+            }
+            if (quad >= 2) {   // dV rows
+                const int t = row - 64;
+                float x[32];
+                tc::tmem_ld32(lane_addr + T_GD + hsel * 32, x);
+                tc::tmem_wait_ld();
+                if (t < n) {
+                    __nv_bfloat16* dst = dv + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&x[c * 8]);
+                }
+            } else {           // state-gradient carry and its exact anchor for the decay gradient
+                float x[32];
+                tc::tmem_ld32(lane_addr + T_TMP + hsel * 32, x);
+                tc::tmem_wait_ld();
+                float pr[32];
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const int c = hsel * 32 + c4 * 4;
+                    float4 old = *reinterpret_cast<const float4*>(&dsf[row * LF_PITCH + c]);
+                    const float4 l4 = *reinterpret_cast<const float4*>(&sm.lam[c]);
+                    old.x = fmaf(old.x, l4.x, x[c4 * 4 + 0]); old.y = fmaf(old.y, l4.y, x[c4 * 4 + 1]);
+                    old.z = fmaf(old.z, l4.z, x[c4 * 4 + 2]); old.w = fmaf(old.w, l4.w, x[c4 * 4 + 3]);
+                    *reinterpret_cast<float4*>(&dsf[row * LF_PITCH + c]) = old;
+                    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (s0src != nullptr) s4 = *reinterpret_cast<const float4*>(s0src + row * kN + c);
+                    pr[c4 * 4 + 0] = old.x * s4.x; pr[c4 * 4 + 1] = old.y * s4.y;
+                    pr[c4 * 4 + 2] = old.z * s4.z; pr[c4 * 4 + 3] = old.w * s4.w;
+                }
+                // column sums over the 32 rows of this warp: fold halves, lane l ends with column l
+#pragma unroll
+                for (int sh = 16; sh >= 1; sh >>= 1) {
+#pragma unroll
+                    for (int e = 0; e < sh; ++e) {
+                        const bool up = (lane & sh) != 0;
+                        const float send = up ? pr[e] : pr[e + sh];
+                        const float keep = up ? pr[e + sh] : pr[e];
+                        pr[e] = keep + __shfl_xor_sync(0xffffffffu, send, sh);
+                    }
+                }
+                // after the folds lane l holds the sum for column bitreverse-free index: see below
+                int col = 0;
+#pragma unroll
+                for (int sh = 16; sh >= 1; sh >>= 1) col += (lane & sh) ? sh : 0;
+                sm.d_part[quad][hsel * 32 + col] = pr[0];
+            }
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            // ================= R5: [dK~';dB~'] and [dR~';dA~'] =================
+            if (tid == 0) {
+                tc::fence_after_sync();
+                mma_k64(tbase + T_KB, kmaj128(sWSA), mnmaj128(sAR), ID_KM, false);
+                mma_k64(tbase + T_KB, kmaj128(sWY), mnmaj128(sAR + HALF), ID_KM, true);
+                mma_k64(tbase + T_KB, kmaj128(sVSA), mnmaj64(sDSL), ID_KM, true);
+                mma_k64(tbase + T_G, kmaj128(sDD), mnmaj64(sS0), ID_KM, false);
+                mma_k64(tbase + T_G, mnmaj128(sWY + HALF), mnmaj128(sBK), ID_MM, true);
+                mma_k64(tbase + T_G, mnmaj128(sWY), mnmaj128(sBK + HALF), ID_MM, true);
+                tc::commit(&sm.bar[4]);
+            }
+            if (!tc::mbar_wait(&sm.bar[4], par)) failed = true;
+            tc::fence_after_sync();
+            float p3[32];   // a_t da_t for the rows that own da
+            {
+                const int t = row & 63;
+                float x[32], z[32];
+                tc::tmem_ld32(lane_addr + T_KB + hsel * 32, x);
+                tc::tmem_ld32(lane_addr + T_G + hsel * 32, z);
+                tc::tmem_wait_ld();
+                float u[32], lwt[32];
+                {
+                    // this row's cumulative log-decay, the previous row's, and the two operand rows it pairs with
+                    float cr[32], cp[32], s1[32], s2[32];
+                    const unsigned char* slab1 = smem + OFF_AR + ((row < 64) ? (64 + t) * 16 : t * 16);   // R~ / A~
+                    const unsigned char* slab2 = smem + OFF_BK + ((row < 64) ? (64 + t) * 16 : t * 16);   // K~ / B~
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const int c = hsel * 32 + c4 * 4;
+                        *reinterpret_cast<float4*>(&cr[c4 * 4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + c]);
+                        *reinterpret_cast<float4*>(&cp[c4 * 4]) = (t & 31) ? *reinterpret_cast<const float4*>(&cum[(t - 1) * LF_PITCH + c])
+                                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        unpack8(*reinterpret_cast<const uint4*>(slab1 + (hsel * 4 + c8) * CB128), &s1[c8 * 8]);
+                        unpack8(*reinterpret_cast<const uint4*>(slab2 + (hsel * 4 + c8) * CB128), &s2[c8 * 8]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int c = hsel * 32 + e;
+                        const float cc = fmaxf(cr[e] + (t >= 32 ? sm.h1[c] : 0.f), kCumFloor);
+                        lwt[e] = cr[e] - cp[e];
+                        const float eI = __expf(-cc);
+                        if (row < 64) {          // dk, dr ; u = r dr - k dk
+                            u[e] = s1[e] * z[e] - s2[e] * x[e];
+                            x[e] *= eI;
+                            z[e] *= __expf(cc);
+                        } else {                 // db, da ; u = a da - b db
+                            p3[e] = s1[e] * z[e];
+                            u[e] = p3[e] - s2[e] * x[e];
+                            x[e] *= eI;
+                            z[e] *= __expf(fminf(fmaxf(cc - lwt[e], kCumFloor), 0.f));
+                        }
+                    }
+                }
+                if (t < n) {
+                    const size_t g = seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+                    __nv_bfloat16* dx = (row < 64) ? dk : db;
+                    __nv_bfloat16* dz = (row < 64) ? dr : da;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        *reinterpret_cast<uint4*>(dx + g + c * 8) = pack8(&x[c * 8]);
+                        *reinterpret_cast<uint4*>(dz + g + c * 8) = pack8(&z[c * 8]);
+                    }
+                }
+                // u_t = (r dr - k dk) + (a da - b db): first the dk/dr rows write, then the db/da rows add
+                if (row < 64) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4)
+                        *reinterpret_cast<float4*>(&lf[t * LF_PITCH + hsel * 32 + c4 * 4]) =
+                            make_float4(u[c4 * 4], u[c4 * 4 + 1], u[c4 * 4 + 2], u[c4 * 4 + 3]);
+                }
+                __syncthreads();
+                if (row >= 64) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        float4 o = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + hsel * 32 + c4 * 4]);
+                        o.x += u[c4 * 4]; o.y += u[c4 * 4 + 1]; o.z += u[c4 * 4 + 2]; o.w += u[c4 * 4 + 3];
+                        *reinterpret_cast<float4*>(&lf[t * LF_PITCH + hsel * 32 + c4 * 4]) = o;
+                    }
+                }
+                __syncthreads();
+                if (tid < 64) {   // D_{t-1} = D_t + u_t, from the carried D at the chunk end
+                    float D = sm.d_in[tid];
+                    for (int tt = 63; tt >= 0; --tt) {
+                        D += lf[tt * LF_PITCH + tid];
+                        lf[tt * LF_PITCH + tid] = D;
+                    }
+                    // carry for the previous chunk: the exact anchor, or zero across a start flag
+                    sm.d_in[tid] = reset_here ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
+                }
+                __syncthreads();
+                if (row >= 64 && t < n) {
+                    float o[32];
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 d4 = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + hsel * 32 + c4 * 4]);
+                        o[c4 * 4 + 0] = (d4.x - p3[c4 * 4 + 0]) * lwt[c4 * 4 + 0];
+                        o[c4 * 4 + 1] = (d4.y - p3[c4 * 4 + 1]) * lwt[c4 * 4 + 1];
+                        o[c4 * 4 + 2] = (d4.z - p3[c4 * 4 + 2]) * lwt[c4 * 4 + 2];
+                        o[c4 * 4 + 3] = (d4.w - p3[c4 * 4 + 3]) * lwt[c4 * 4 + 3];
+                    }
+                    if (reset_here && t == 0) {   // the state entering a start token is zero: no decay gradient
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = 0.f;
+                    }
+                    __nv_bfloat16* dst = dw + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&o[c * 8]);
+                }
+            }
+            if (reset_here) {
+                __syncthreads();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) dsf[si * LF_PITCH + scq * 16 + e] = 0.f;
+            }
+            tc::fence_before_sync();
+            p1 = p;
+            par ^= 1u;
+        }
+    }
+    __syncthreads();
+    {   // gradient with respect to the initial state
+        float g[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) g[e] = dsf[si * LF_PITCH + scq * 16 + e];
+        if (L == 0 && ds_out != nullptr) {
+            float o[16];
+            unpack8(*reinterpret_cast<const uint4*>(ds_out + st_base + si * kN + scq * 16), o);
+            unpack8(*reinterpret_cast<const uint4*>(ds_out + st_base + si * kN + scq * 16 + 8), o + 8);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) g[e] += o[e];
+        }
+        *reinterpret_cast<uint4*>(ds0 + st_base + si * kN + scq * 16) = pack8(g);
+        *reinterpret_cast<uint4*>(ds0 + st_base + si * kN + scq * 16 + 8) = pack8(g + 8);
+    }
+    if (failed && status != nullptr) atomicExch(status, 2);
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tbase, 512);
+}
+
+}  // namespace
+
+int* wkv7_chunk_status_word();
+
+int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
+                   const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
+                   const void* ds_out, const void* residual, void* dw, void* dr, void* dk, void* dv, void* da,
+                   void* db, void* ds0) {
+    typedef __nv_bfloat16 bf;
+    if (cudaFuncSetAttribute(wkv7_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        return B200WKV_ELAUNCH;
+    const float* ck = (const float*)residual;
+    const float* sl = ck + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN;
+    wkv7_chunk_bwd_kernel<<<B * H, 256, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
+                                                          (const bf*)a, (const bf*)b, length, ns, (const bf*)dy,
+                                                          (const bf*)ds_out, ck, sl, (bf*)dw, (bf*)dr, (bf*)dk,
+                                                          (bf*)dv, (bf*)da, (bf*)db, (bf*)ds0, wkv7_chunk_status_word());
+    return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+}
+
+}  // namespace b200wkv

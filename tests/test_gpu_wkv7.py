@@ -11,6 +11,10 @@ from gpu_util import NAMES7, TOL, to_dev, rounded, flags, npf, wkv7_case
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
+# (element type, flags): fp32 -> sequential kernels; bf16 -> chunked tensor-core kernels, or the
+# sequential ones when B200WKV_FLAG_SEQUENTIAL is set
+KERNELS = [pytest.param(torch.float32, 0, id="f32-seq"), pytest.param(torch.bfloat16, 0, id="bf16-chunk"),
+           pytest.param(torch.bfloat16, _lib.FLAG_SEQUENTIAL, id="bf16-seq")]
 
 
 def run_fwd(t, length, ns, flags_=0):
@@ -95,24 +99,39 @@ def test_fwd_config2_shape_bf16():
     check_fwd(d, torch.bfloat16)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T", [1, 7, 8, 9, 16, 17, 24, 33, 70])
-def test_bwd_ragged(T, dtype):
+@pytest.mark.parametrize("dtype,kflags", KERNELS)
+@pytest.mark.parametrize("T", [1, 7, 8, 9, 16, 17, 24, 33, 64, 70, 130])
+def test_bwd_ragged(T, dtype, kflags):
     rng = np.random.default_rng(T)
     starts = [sorted(set(rng.integers(0, T, size=2).tolist())), [0], [T // 2, min(T // 2 + 1, T - 1)]]
     lengths = [T, max(T - 3, 0), 0]
-    check_bwd(wkv7_case(3, T, 2, seed=200 + T, s0_scale=0.5, starts=starts, lengths=lengths), dtype)
+    check_bwd(wkv7_case(3, T, 2, seed=200 + T, s0_scale=0.5, starts=starts, lengths=lengths), dtype, flags_=kflags)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_bwd_missing_cotangents(dtype):
+@pytest.mark.parametrize("dtype,kflags", KERNELS)
+def test_bwd_missing_cotangents(dtype, kflags):
     d = wkv7_case(2, 40, 2, seed=9, s0_scale=0.5, starts=[[0, 20], [3]], lengths=[33, 40])
-    check_bwd(d, dtype, use_gy=True, use_gs=False)
-    check_bwd(d, dtype, use_gy=False, use_gs=True)
+    check_bwd(d, dtype, use_gy=True, use_gs=False, flags_=kflags)
+    check_bwd(d, dtype, use_gy=False, use_gs=True, flags_=kflags)
 
 
-def test_bwd_training_shape_bf16():
-    check_bwd(wkv7_case(2, 512, 4, seed=11, p_start=1 / 128, random_length=True, s0_scale=0.1), torch.bfloat16)
+def test_bwd_chunk_single_full_chunk_no_state():
+    """Smallest tensor-core case: one 64-token chunk, zero initial state, start at t=0."""
+    check_bwd(wkv7_case(1, 64, 1, seed=51), torch.bfloat16)
+
+
+def test_bwd_chunk_carried_state_two_chunks():
+    check_bwd(wkv7_case(1, 128, 1, seed=52, s0_scale=0.5, starts=[[]], lengths=[128]), torch.bfloat16)
+
+
+def test_bwd_chunk_adjacent_starts():
+    T = 70
+    check_bwd(wkv7_case(2, T, 1, seed=53, s0_scale=1.0, starts=[range(T), [7, 8, 9, 24, 25, 64, 65]], lengths=[T, 66]), torch.bfloat16)
+
+
+@pytest.mark.parametrize("kflags", [0, _lib.FLAG_SEQUENTIAL])
+def test_bwd_training_shape_bf16(kflags):
+    check_bwd(wkv7_case(2, 512, 4, seed=11, p_start=1 / 128, random_length=True, s0_scale=0.1), torch.bfloat16, flags_=kflags)
 
 
 def test_bwd_config1_fp32():
@@ -137,22 +156,22 @@ def test_operator_autograd_and_vmap_on_gpu():
     assert torch.equal(y2[0], y2[1]) and torch.equal(y2[0], y2[2]) and torch.equal(s2[0], s2[2])
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_run_to_run_determinism(dtype):
+@pytest.mark.parametrize("dtype,kflags", KERNELS)
+def test_run_to_run_determinism(dtype, kflags):
     d = wkv7_case(2, 100, 2, seed=31, p_start=0.05, s0_scale=0.3)
     t = to_dev(d, dtype)
     length, ns = flags(d)
     outs = []
     for _ in range(2):
-        s, y, res = run_fwd(t, length, ns)
-        g = rwkv7.batched_wkv7_bwd(res, (s.clone(), y.clone()), 2)
+        s, y, res = run_fwd(t, length, ns, kflags)
+        g = rwkv7.batched_wkv7_bwd(res, (s.clone(), y.clone()), 2, flags=kflags)
         outs.append((s, y) + tuple(g))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
 
 
 def test_full_size_properties_bf16():
-    """Headline shape B=8, T=4096, H=32, bf16.  Size-independent properties instead of an
+    """Headline shape B=8, T=4096, H=32, bf16, sequential kernel.  Size-independent properties instead of an
     oracle run: (1) a start flag at t splits the sequence into independent parts, so the
     tail equals a separate call on the tail; (2) y and s_out are linear in (v, s0), and
     scaling by 2 is exact in binary floating point, so the results must be bit-identical
@@ -163,17 +182,18 @@ def test_full_size_properties_bf16():
     d["new_starts"][:, 1500] = True
     t = to_dev(d, torch.bfloat16)
     length, ns = flags(d)
-    s, y, _ = run_fwd(t, length, ns)
+    SEQ = _lib.FLAG_SEQUENTIAL
+    s, y, _ = run_fwd(t, length, ns, SEQ)
     assert torch.isfinite(y.float()).all() and torch.isfinite(s.float()).all()
     # (1) tail after the start flag == fresh call on the tail with any initial state
     tail = {n: t[n][:, 1500:].contiguous() for n in NAMES7[:-1]}
     tail["s0"] = torch.randn_like(t["s0"])
     ns_tail = ns[:, 1500:].contiguous()
-    s_t, y_t, _ = run_fwd(tail, torch.full((B,), T - 1500), ns_tail)
+    s_t, y_t, _ = run_fwd(tail, torch.full((B,), T - 1500), ns_tail, SEQ)
     assert torch.equal(y_t, y[:, 1500:]) and torch.equal(s_t, s)
     # (2) exact homogeneity in (v, s0)
     t2 = dict(t); t2["v"] = t["v"] * 2; t2["s0"] = t["s0"] * 2
-    s2, y2, _ = run_fwd(t2, length, ns)
+    s2, y2, _ = run_fwd(t2, length, ns, SEQ)
     assert torch.equal(y2, y * 2) and torch.equal(s2, s * 2)
     # (3) state carry across calls, in fp32 so that the hand-over is not rounded
     B3, H3 = 2, 4
@@ -286,3 +306,29 @@ def test_chunk_fwd_full_size_properties():
     # sequential kernel on the same inputs
     s_q, y_q, _ = run_fwd(t, length, ns, _lib.FLAG_SEQUENTIAL)
     assert rel_err(npf(y), npf(y_q)) < TOL[torch.bfloat16] and rel_err(npf(s), npf(s_q)) < TOL[torch.bfloat16]
+
+
+def test_chunk_bwd_full_size_properties():
+    """Headline shape through the tensor-core forward + backward: finite, deterministic, and the
+    gradients are exactly homogeneous of degree one in the cotangents (scaling dy and ds by 2)."""
+    B, T, H = 8, 4096, 32
+    d = wkv7_case(B, T, H, seed=1239, s0_scale=0.1, p_start=1 / 512)
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    s, y, res = run_fwd(t, length, ns)
+    gy = torch.randn_like(y); gs = torch.randn_like(s)
+    g1 = rwkv7.batched_wkv7_bwd(res, (gs, gy), B)
+    g1b = rwkv7.batched_wkv7_bwd(res, (gs, gy), B)
+    g2 = rwkv7.batched_wkv7_bwd(res, (gs * 2, gy * 2), B)
+    for a, b, c in zip(g1, g1b, g2):
+        assert torch.isfinite(a.float()).all()
+        assert torch.equal(a, b)
+        assert torch.equal(c, a * 2)
+    # spot-check two (batch, head) slices against the oracle
+    for bi, hh in ((0, 0), (7, 31)):
+        ins = [t[n][bi:bi + 1, :, hh:hh + 1].double().cpu().numpy() for n in NAMES7[:-1]] + [t["s0"][bi:bi + 1, hh:hh + 1].double().cpu().numpy()]
+        ref = oracle.wkv7_bwd_batched(*ins, d["length"][bi:bi + 1], d["new_starts"][bi:bi + 1],
+                                      npf(gy[bi:bi + 1, :, hh:hh + 1]), npf(gs[bi:bi + 1, hh:hh + 1]))
+        got = [g1[i][bi:bi + 1, :, hh:hh + 1] for i in range(6)] + [g1[6][bi:bi + 1, hh:hh + 1]]
+        for n, a, b in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), got, ref):
+            assert rel_err(npf(a), b) < TOL[torch.bfloat16], (n, bi, hh, rel_err(npf(a), b))
