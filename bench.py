@@ -163,6 +163,7 @@ def main():
     import torch
     import torch.distributed as dist
     from jaxrwkv_b200 import rwkv7, _lib
+    from jaxrwkv_b200.shard import max_over_ranks
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -213,10 +214,7 @@ def main():
     ms_total = t_begin.elapsed_time(t_end)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
-    tm = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-    ms_step = float(tm.item()) / args.steps
+    ms_step = max_over_ranks(ms_total, dev) / args.steps
     tokens = B * T * world
     value = tokens / (ms_step / 1e3)
 
@@ -251,12 +249,10 @@ def main():
             e2e_step()
         e1.record()
         barrier()
-        te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        te_ms = max_over_ranks(e0.elapsed_time(e1), dev)
         h2d = sum(host_in[n].numel() * host_in[n].element_size() for n in names_in)
         d2h = sum(h.numel() * h.element_size() for h in host_out)
-        e2e = {"value": tokens / (float(te.item()) / e_steps / 1e3), "unit": "tokens/s",
+        e2e = {"value": tokens / (te_ms / e_steps / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e_steps}
 
     if rank != 0:
