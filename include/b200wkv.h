@@ -89,6 +89,33 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N,
                  void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
                  unsigned flags);
 
+/* Forward + backward in one call with NO residual buffer from the caller (no counterpart in
+ * jaxrwkv: its kernels always take the residuals as operands).
+ *
+ * For hosts that cannot allocate device memory where they need the gradients - e.g. a
+ * custom-call handler inside a compiled program whose layer body is rematerialised, so the
+ * forward is re-run during the backward pass and the framework's memory pool, not the handler,
+ * owns every device byte.  The state checkpoints live in a fixed array inside the library image
+ * (b200wkv7_static_scratch_bytes() bytes, 64 MiB, held by every GPU that loads the library until
+ * the process exits).  Problems whose b200wkv7_residual_bytes() exceeds that size are refused
+ * with B200WKV_ESCRATCH and nothing is launched.  The call itself never calls cudaMalloc/cudaFree
+ * or any allocating routine; the first call on each device resolves the array's device address
+ * (make that first call before starting a stream capture on that device).  All calls on a device
+ * share the one array and it keeps the previous call's contents (nothing in it needs clearing: the
+ * forward rewrites every slot the backward reads), so two calls must not overlap on the GPU -
+ * issue them on one stream or order them with events.
+ * Results equal b200wkv7_fwd followed by b200wkv7_bwd with the same dtype and flags. */
+size_t b200wkv7_static_scratch_bytes(void);
+
+int b200wkv7_fwd_bwd_static(void* stream, int dtype, int B, int T, int H, int N,
+                            const void* w, const void* r, const void* k, const void* v,
+                            const void* a, const void* b, const void* s0,
+                            const uint32_t* length, const uint8_t* new_starts,
+                            const void* dy, const void* ds_out,
+                            void* y, void* s_out,
+                            void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
+                            unsigned flags);
+
 #ifdef __cplusplus
 }
 #endif

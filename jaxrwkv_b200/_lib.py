@@ -20,6 +20,8 @@ PROTOTYPES = {
     "b200wkv7_residual_bytes": (_SZ, [_I, _I, _I, _I, _I]),
     "b200wkv7_fwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ, _U]),
     "b200wkv7_bwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ] + [_P] * 7 + [_U]),
+    "b200wkv7_static_scratch_bytes": (_SZ, []),
+    "b200wkv7_fwd_bwd_static": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P] + [_P, _P] + [_P] * 7 + [_U]),
 }
 
 _lib = None
