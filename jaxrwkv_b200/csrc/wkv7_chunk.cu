@@ -26,20 +26,21 @@ namespace b200wkv {
 
 namespace {
 
-
-// shared-memory map (bytes)
-constexpr int OFF_AR = 0;                        // [A~ ; R~]           128-row slab   (LF aliases AR+BK)
-constexpr int OFF_BK = OFF_AR + SLAB128;         // [B~ ; K~]           128-row slab
-constexpr int OFF_BH = OFF_BK + SLAB128;         // B^                  64-row slab
+// shared-memory map (bytes); two CTAs per SM
+constexpr int OFF_AR = 0;                        // [A~ ; R~]           128-row slab  } dead once the first
+constexpr int OFF_BK = OFF_AR + SLAB128;         // [B~ ; K~]           128-row slab  } products are done:
+constexpr int OFF_S0 = OFF_BK + SLAB128;         // S0 in bf16          64-row slab   } LF, X, SCR alias them
+constexpr int OFF_BH = OFF_S0 + SLAB64;          // B^                  64-row slab
 constexpr int OFF_KH = OFF_BH + SLAB64;          // K^                  64-row slab
 constexpr int OFF_SA = OFF_KH + SLAB64;          // sa                  64-row slab   } consecutive: the MN-major
 constexpr int OFF_V = OFF_SA + SLAB64;           // V                   64-row slab   } A operands of the state
 constexpr int OFF_M2A = OFF_V + SLAB64;          // [A_ak ; P_rk]       128-row slab  } update span two slabs
 constexpr int OFF_G = OFF_M2A;                   // G (aliases M2A once the A_ak/P_rk product is done)
 constexpr int OFF_TP = OFF_M2A + SLAB128;        // [Tinv ; P_rb]       128-row slab   (CUM aliases TP)
-constexpr int OFF_S0 = OFF_TP + SLAB128;         // S0 in bf16          64-row slab
-constexpr int OFF_SMALL = OFF_S0 + SLAB64;
-constexpr int OFF_LF = OFF_AR;
+constexpr int OFF_SMALL = OFF_TP + LF_PITCH * 64 * 4;   // TP is 16512 B; the scan buffer that aliases it needs 17408
+constexpr int OFF_LF = OFF_AR;                           // fp32 A_ab
+constexpr int OFF_X = OFF_LF + LF_PITCH * 64 * 4;        // fp32 (I - A_ab)^-1
+constexpr int OFF_SCR = OFF_X + LF_PITCH * 64 * 4;       // scratch of the inverse
 constexpr int OFF_CUM = OFF_TP;
 struct Small {
     float h1[kN];        // cumulative log-decay of tokens 0..31
@@ -50,27 +51,30 @@ struct Small {
     uint32_t tmem;
 };
 constexpr int SMEM_BYTES = OFF_SMALL + (int)sizeof(Small);
-static_assert(LF_PITCH * 64 * 4 <= 2 * SLAB128, "triangular matrix must fit over AR+BK");
-static_assert(64 * 64 * 4 <= SLAB128, "cumulative-sum buffer must fit over TP");
+static_assert(OFF_SCR + TRI_SCR_FLOATS * 4 <= OFF_BH, "inverse work space must fit over AR+BK+S0");
+static_assert(2 * (SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs per SM");
 
 __device__ int g_status;  // last device-side error (0 = none); see wkv7_chunk_status()
 
-__global__ void __launch_bounds__(128, 2)
+// 256 threads: warp = (quad, hsel); quad selects the 32 TMEM lanes (tile rows) the warp may access,
+// hsel the column half it works on, so every accumulator tile is shared by two warps per row group.
+__global__ void __launch_bounds__(256, 2)
 wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ r,
                       const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                       const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
-                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
-                      float* __restrict__ dbg) {
+                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hsel = warp >> 2;
+    const int row = quad * 32 + lane;
     const int L = min((int)length[bi], Tlen);
     const size_t tok_stride = (size_t)H * kN;
     const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
-    const size_t st_row = ((size_t)bh * kN + (tid & 63)) * kN;  // this thread's state row (threads 0..63)
+    const size_t st_row = ((size_t)bh * kN + (row & 63)) * kN + hsel * 32;  // this thread's 32 state elements
     const int nBlk = (Tlen + kC - 1) / kC;
 
     if (tid == 0) {
@@ -83,22 +87,21 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tbase = sm.tmem;
-    const uint32_t lane_addr = tbase + ((uint32_t)(warp * 32) << 16);  // this warp's 32 TMEM lanes
+    const uint32_t lane_addr = tbase + ((uint32_t)(quad * 32) << 16);  // this warp's 32 TMEM lanes
     const uint32_t D1 = 0, D2 = 128, DS = 192;                        // TMEM column offsets (D3 aliases D1)
     bool failed = false;
 
     // ---- state into TMEM (rows 0..63 = S0 in fp32, rows 64..127 are never read) --------------
     {
-        float s[64];
-        if (tid < 64) {
+        float s[32];
+        if (row < 64) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) unpack8(*reinterpret_cast<const uint4*>(s0 + st_row + c * 8), &s[c * 8]);
+            for (int c = 0; c < 4; ++c) unpack8(*reinterpret_cast<const uint4*>(s0 + st_row + c * 8), &s[c * 8]);
         } else {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) s[c] = 0.f;
+            for (int c = 0; c < 32; ++c) s[c] = 0.f;
         }
-        tc::tmem_st32(lane_addr + DS, s);
-        tc::tmem_st32(lane_addr + DS + 32, s + 32);
+        tc::tmem_st32(lane_addr + DS + hsel * 32, s);
         tc::tmem_wait_st();
     }
 
@@ -112,9 +115,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     constexpr uint32_t ID_128x64_KM = tc::make_idesc(128, 64, false, true);
     constexpr uint32_t ID_128x64_MM = tc::make_idesc(128, 64, true, true);
 
-    float* cum = reinterpret_cast<float*>(smem + OFF_CUM);  // [64][64]
+    float* cum = reinterpret_cast<float*>(smem + OFF_CUM);  // [64][LF_PITCH]
     float* lf = reinterpret_cast<float*>(smem + OFF_LF);    // [64][LF_PITCH]
-    const int tsub = tid >> 3, jb = tid & 7;                // staging unit: tokens 16q+tsub, channels 8jb..8jb+7
+    float* xinv = reinterpret_cast<float*>(smem + OFF_X);   // [64][LF_PITCH]
+    float* scr = reinterpret_cast<float*>(smem + OFF_SCR);
+    const int tsub = tid >> 3, jb = tid & 7;                // staging unit: tokens 32q+tsub (q=0,1), channels 8jb..8jb+7
 
     int p = 0;
     uint32_t par = 0;
@@ -122,24 +127,23 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= boundary at position p: TMEM holds the state after token p-1 =================
         const bool want_out = (p == L);
         const bool want_ck = (ckpt != nullptr) && (p % kC == 0) && (p < Tlen);
-        if (tid < 64 && (want_out || want_ck)) {
-            float s[64];
-            tc::tmem_ld32(lane_addr + DS, s);
-            tc::tmem_ld32(lane_addr + DS + 32, s + 32);
+        if (quad < 2 && (want_out || want_ck)) {
+            float s[32];
+            tc::tmem_ld32(lane_addr + DS + hsel * 32, s);
             tc::tmem_wait_ld();
             if (want_out) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(s_out + st_row + c * 8) = pack8(&s[c * 8]);
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(s_out + st_row + c * 8) = pack8(&s[c * 8]);
                 if (s_at_len != nullptr) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c)
+                    for (int c = 0; c < 8; ++c)
                         *reinterpret_cast<float4*>(s_at_len + st_row + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
                 }
             }
             if (want_ck) {
-                float* dst = ckpt + (((size_t)bh * nBlk + p / kC) * kN + tid) * kN;
+                float* dst = ckpt + (((size_t)bh * nBlk + p / kC) * kN + row) * kN + hsel * 32;
 #pragma unroll
-                for (int c = 0; c < 16; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
             }
         }
         if (p >= Tlen) break;
@@ -152,9 +156,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             const uint32_t m = __ballot_sync(0xffffffffu, f);
             if (lane == 0) sm.nsm[warp] = m;
         }
-        // ================= stage inputs (registers) =================
-        uint4 raw[4][5];   // r, k, v, a, b
-        float lw[4][8];    // log-decay  -exp(w)
         __syncthreads();   // nsm visible; previous chunk's shared-memory readers are done
         const uint64_t mask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
         const bool reset_here = (mask & 1ull) != 0;
@@ -162,9 +163,12 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if ((mask >> 1) != 0) p1 = p + __ffsll((long long)(mask >> 1));
         if (L > p && L < p1) p1 = L;
         const int n = p1 - p;
+        // ================= stage inputs (registers), log-decay into the scan buffer =================
+        uint4 raw[2][5];   // r, k, v, a, b
+        float lw[2][8];    // log-decay  -exp(w)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int t = q * 16 + tsub;
+        for (int q = 0; q < 2; ++q) {
+            const int t = q * 32 + tsub;
             if (t < n) {
                 const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
                 float wf[8];
@@ -182,18 +186,24 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
                 for (int e = 0; e < 8; ++e) lw[q][e] = 0.f;
             }
-            *reinterpret_cast<float4*>(&cum[t * 64 + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
-            *reinterpret_cast<float4*>(&cum[t * 64 + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
+            *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
+            *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
+            // pull the lines of the next 64 tokens towards L2 (one thread per 128-byte line)
+            if (jb == 0 && p + kC + t < Tlen) {
+                const size_t gn = seq_base + (size_t)(p + kC + t) * tok_stride;
+                prefetch_l2(w + gn); prefetch_l2(r + gn); prefetch_l2(k + gn);
+                prefetch_l2(v + gn); prefetch_l2(a + gn); prefetch_l2(b + gn);
+            }
         }
         __syncthreads();
-        {   // inclusive scan over tokens, two independent halves of 32 per channel
+        if (tid < 128) {   // inclusive scan over tokens, two independent halves of 32 per channel
             const int j = tid & 63, half = tid >> 6;
             float run = 0.f;
 #pragma unroll 8
             for (int tt = 0; tt < 32; ++tt) {
                 const int t = half * 32 + tt;
-                run += cum[t * 64 + j];
-                cum[t * 64 + j] = run;
+                run += cum[t * LF_PITCH + j];
+                cum[t * LF_PITCH + j] = run;
             }
             if (half == 0) sm.h1[j] = run;
             else sm.tot[j] = run;   // second-half sum for now
@@ -211,19 +221,19 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
             for (int e = 0; e < 8; ++e) { h1v[e] = sm.h1[jb * 8 + e]; totv[e] = sm.tot[jb * 8 + e]; }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int t = q * 16 + tsub;
+            for (int q = 0; q < 2; ++q) {
+                const int t = q * 32 + tsub;
                 float c[8];
-                *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * 64 + jb * 8]);
-                *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * 64 + jb * 8 + 4]);
+                *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8]);
+                *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8 + 4]);
                 float rf[8], kf[8], af[8], bf[8], o[8];
                 unpack8(raw[q][0], rf); unpack8(raw[q][1], kf); unpack8(raw[q][3], af); unpack8(raw[q][4], bf);
                 float eL[8], eI[8], eP[8], eE[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float cc = fmaxf(c[e] + (q >= 2 ? h1v[e] : 0.f), kCumFloor);
-                    const float cp = fmaxf(cc - lw[q][e], kCumFloor);   // cumulative log-decay before this token
-                    eL[e] = __expf(cc); eI[e] = __expf(-cc); eP[e] = __expf(fminf(cp, 0.f)); eE[e] = __expf(totv[e] - cc);
+                    const float cc = fmaxf(c[e] + (q == 1 ? h1v[e] : 0.f), kCumFloor);
+                    const float cp = fminf(fmaxf(cc - lw[q][e], kCumFloor), 0.f);   // cumulative log-decay before this token
+                    eL[e] = __expf(cc); eI[e] = __expf(-cc); eP[e] = __expf(cp); eE[e] = __expf(totv[e] - cc);
                 }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) o[e] = af[e] * eP[e];
@@ -247,25 +257,23 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
         // ================= entering state: bf16 copy for the products, decayed fp32 copy back to TMEM =====
-        if (tid < 64) {
-            float s[64];
+        if (quad < 2) {
+            float s[32];
             if (reset_here) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) s[c] = 0.f;
+                for (int c = 0; c < 32; ++c) s[c] = 0.f;
             } else {
-                tc::tmem_ld32(lane_addr + DS, s);
-                tc::tmem_ld32(lane_addr + DS + 32, s + 32);
+                tc::tmem_ld32(lane_addr + DS + hsel * 32, s);
                 tc::tmem_wait_ld();
             }
 #pragma unroll
-            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_S0, CB64, tid, c, pack8(&s[c * 8]));
+            for (int c = 0; c < 4; ++c) slab_store(smem + OFF_S0, CB64, row, hsel * 4 + c, pack8(&s[c * 8]));
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float4 l4 = *reinterpret_cast<const float4*>(&sm.lam[c * 4]);
+            for (int c = 0; c < 8; ++c) {
+                const float4 l4 = *reinterpret_cast<const float4*>(&sm.lam[hsel * 32 + c * 4]);
                 s[c * 4] *= l4.x; s[c * 4 + 1] *= l4.y; s[c * 4 + 2] *= l4.z; s[c * 4 + 3] *= l4.w;
             }
-            tc::tmem_st32(lane_addr + DS, s);
-            tc::tmem_st32(lane_addr + DS + 32, s + 32);
+            tc::tmem_st32(lane_addr + DS + hsel * 32, s);
             tc::tmem_wait_st();
         }
         tc::fence_async_smem();
@@ -288,33 +296,26 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_after_sync();
         // ================= E1: triangular masks, operands of the next products =================
         {
-            const int t = tid & 63;
+            const int t = row & 63;
             float d[64];
-            // columns 0..63: A_ab (rows 0..63) / P_rb (rows 64..127)
-            tc::tmem_ld32(lane_addr + D1, d);
-            tc::tmem_ld32(lane_addr + D1 + 32, d + 32);
+            tc::tmem_ld32(lane_addr + D1 + hsel * 64, d);
+            tc::tmem_ld32(lane_addr + D1 + hsel * 64 + 32, d + 32);
             tc::tmem_wait_ld();
-            if (tid < 64) {
+            if (row < 64 && hsel == 0) {          // A_ab, strictly lower, fp32 for the inverse
 #pragma unroll
                 for (int c = 0; c < 16; ++c)
                     *reinterpret_cast<float4*>(&lf[t * LF_PITCH + c * 4]) =
                         make_float4(c * 4 + 0 < t ? d[c * 4 + 0] : 0.f, c * 4 + 1 < t ? d[c * 4 + 1] : 0.f,
                                     c * 4 + 2 < t ? d[c * 4 + 2] : 0.f, c * 4 + 3 < t ? d[c * 4 + 3] : 0.f);
             } else {
+                const int lim = (row < 64) ? t : t + 1;   // A_ak strict; P_rb, P_rk inclusive
 #pragma unroll
-                for (int s = 0; s < 64; ++s) d[s] = (s <= t) ? d[s] : 0.f;
+                for (int s = 0; s < 64; ++s) d[s] = (s < lim) ? d[s] : 0.f;
+                // A_ak -> M2A rows 0..63, P_rk -> M2A rows 64..127, P_rb -> TP rows 64..127
+                unsigned char* dst = smem + ((hsel == 1) ? OFF_M2A : OFF_TP);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) slab_store(smem + OFF_TP, CB128, 64 + t, c, pack8(&d[c * 8]));
+                for (int c = 0; c < 8; ++c) slab_store(dst, CB128, row, c, pack8(&d[c * 8]));
             }
-            // columns 64..127: A_ak (rows 0..63, strict) / P_rk (rows 64..127, inclusive)
-            tc::tmem_ld32(lane_addr + D1 + 64, d);
-            tc::tmem_ld32(lane_addr + D1 + 96, d + 32);
-            tc::tmem_wait_ld();
-            const int lim = (tid < 64) ? t : t + 1;   // keep columns s < lim
-#pragma unroll
-            for (int s = 0; s < 64; ++s) d[s] = (s < lim) ? d[s] : 0.f;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_M2A, CB128, tid, c, pack8(&d[c * 8]));
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
@@ -328,43 +329,16 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         tc::make_desc(sV + ks * 256, 128, CB64), ID_128x64_KM, true);
             tc::commit(&sm.bar[1]);
         }
-        if (tid >= 64) {
-            // column c of X = (I - A_ab)^-1 by forward substitution over the rows
-            const int c = tid - 64;
-            float x[64];
-#pragma unroll
-            for (int t = 0; t < 64; ++t) x[t] = 0.f;
-#pragma unroll
-            for (int t = 0; t < 64; ++t) {
-                float a0 = (t == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-                for (int m4 = 0; m4 < (t + 3) / 4; ++m4) {
-                    const float4 l = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + m4 * 4]);
-                    a0 = fmaf(l.x, x[m4 * 4 + 0], a0); a1 = fmaf(l.y, x[m4 * 4 + 1], a1);
-                    a2 = fmaf(l.z, x[m4 * 4 + 2], a2); a3 = fmaf(l.w, x[m4 * 4 + 3], a3);
-                }
-                x[t] = (a0 + a1) + (a2 + a3);
-            }
-            unsigned char* col = smem + OFF_TP + (c >> 3) * CB128 + (c & 7) * 2;
-#pragma unroll
-            for (int t = 0; t < 64; ++t) *reinterpret_cast<__nv_bfloat16*>(col + t * 16) = __float2bfloat16_rn(x[t]);
-            if (dbg != nullptr && bh == 0 && p == 0) {
-#pragma unroll
-                for (int t = 0; t < 64; ++t) dbg[4096 + t * 64 + c] = x[t];
-            }
-        } else {
+        tri_inverse_64<256>(lf, xinv, scr, tid);
+        fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid);
+        if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
             tc::fence_after_sync();
-            float g[64];
-            tc::tmem_ld32(lane_addr + D2, g);
-            tc::tmem_ld32(lane_addr + D2 + 32, g + 32);
+            float g[32];
+            tc::tmem_ld32(lane_addr + D2 + hsel * 32, g);
             tc::tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_G, CB64, tid, c, pack8(&g[c * 8]));
-            if (dbg != nullptr && bh == 0 && p == 0) {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) { dbg[2 * 4096 + tid * 64 + c] = g[c]; dbg[tid * 64 + c] = lf[tid * LF_PITCH + c]; }
-            }
+            for (int c = 0; c < 4; ++c) slab_store(smem + OFF_G, CB64, row, hsel * 4 + c, pack8(&g[c * 8]));
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
@@ -378,19 +352,14 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         tc::make_desc(sG + ks * 256, 128, CB64), ID_128x64_KM, ks > 0);
             tc::commit(&sm.bar[2]);
         }
-        if (tid < 64) {
+        if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[2], par)) failed = true;
             tc::fence_after_sync();
-            float sa[64];
-            tc::tmem_ld32(lane_addr + D1, sa);
-            tc::tmem_ld32(lane_addr + D1 + 32, sa + 32);
+            float sa[32];
+            tc::tmem_ld32(lane_addr + D1 + hsel * 32, sa);
             tc::tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 8; ++c) slab_store(smem + OFF_SA, CB64, tid, c, pack8(&sa[c * 8]));
-            if (dbg != nullptr && bh == 0 && p == 0) {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) dbg[3 * 4096 + tid * 64 + c] = sa[c];
-            }
+            for (int c = 0; c < 4; ++c) slab_store(smem + OFF_SA, CB64, row, hsel * 4 + c, pack8(&sa[c * 8]));
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
@@ -414,20 +383,15 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
-        if (tid >= 64) {
-            const int t = tid - 64;
-            float yv[64];
-            tc::tmem_ld32(lane_addr + D2, yv);
-            tc::tmem_ld32(lane_addr + D2 + 32, yv + 32);
+        if (quad >= 2) {
+            const int t = row - 64;
+            float yv[32];
+            tc::tmem_ld32(lane_addr + D2 + hsel * 32, yv);
             tc::tmem_wait_ld();
             if (t < n) {
-                __nv_bfloat16* dst = y + seq_base + (size_t)(p + t) * tok_stride;
+                __nv_bfloat16* dst = y + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&yv[c * 8]);
-            }
-            if (dbg != nullptr && bh == 0 && p == 0) {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) dbg[4 * 4096 + t * 64 + c] = yv[c];
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&yv[c * 8]);
             }
         }
         tc::fence_before_sync();
@@ -450,11 +414,11 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     typedef __nv_bfloat16 bf;
     if (cudaFuncSetAttribute(wkv7_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
         return B200WKV_ELAUNCH;
-    wkv7_chunk_fwd_kernel<<<B * H, 128, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
+    wkv7_chunk_fwd_kernel<<<B * H, 256, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
                                                           (bf*)y, (bf*)s_out, (float*)residual,
-                                                          residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
-                                                          (float*)dbg);
+                                                          residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr);
+    (void)dbg;
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

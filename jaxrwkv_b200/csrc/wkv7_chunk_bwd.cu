@@ -45,7 +45,9 @@ constexpr int OFF_WSA = OFF_WY + SLAB128;         // [V ; sa] . dsa^T   128-row 
 constexpr int OFF_LF = OFF_X + 4 * SLAB64;        // fp32 A_ab for the inverse; later the decay-gradient scan
 constexpr int OFF_CUM = OFF_LF + LF_PITCH * 64 * 4;   // fp32 cumulative log-decay [64][LF_PITCH]
 constexpr int OFF_DSF = OFF_CUM + LF_PITCH * 64 * 4;   // fp32 dS carried across chunks [64][LF_PITCH]
-constexpr int OFF_SMALL = OFF_DSF + LF_PITCH * 64 * 4;
+constexpr int OFF_XINV = OFF_DSF + LF_PITCH * 64 * 4; // fp32 (I - A_ab)^-1
+constexpr int OFF_SCR = OFF_XINV + LF_PITCH * 64 * 4;    // scratch of the inverse
+constexpr int OFF_SMALL = OFF_SCR + TRI_SCR_FLOATS * 4;
 static_assert(2 * SLAB128 <= 4 * SLAB64, "W must fit over the X region");
 struct Small {
     float h1[kN];
@@ -53,6 +55,7 @@ struct Small {
     float lam[kN];
     float d_in[kN];        // D carried from the chunk processed before (later in time)
     float d_part[2][kN];   // partial column sums of the new anchor
+    float seg[4][kN];      // per-16-token totals of the decay-gradient scan
     uint64_t bar[5];
     uint32_t nsm[2];
     uint32_t tmem;
@@ -197,6 +200,13 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
                 *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
+                // pull the lines of the 64 tokens in front of this chunk (processed next) towards L2
+                if (jb == 0 && p - kC + t >= 0) {
+                    const size_t gn = seq_base + (size_t)(p - kC + t) * tok_stride;
+                    prefetch_l2(w + gn); prefetch_l2(r + gn); prefetch_l2(k + gn); prefetch_l2(v + gn);
+                    prefetch_l2(a + gn); prefetch_l2(b + gn);
+                    if (dy != nullptr) prefetch_l2(dy + gn);
+                }
             }
             __syncthreads();
             if (tid < 128) {
@@ -319,26 +329,9 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_GD, mnmaj64(sPRB), mnmaj128(sDD), ID_MM, true);
                 tc::commit(&sm.bar[1]);
             }
-            if (warp == 2 || warp == 3) {
-                const int c = tid - 64;
-                float x[64];
-#pragma unroll
-                for (int t = 0; t < 64; ++t) x[t] = 0.f;
-#pragma unroll
-                for (int t = 0; t < 64; ++t) {
-                    float a0 = (t == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-                    for (int m4 = 0; m4 < (t + 3) / 4; ++m4) {
-                        const float4 l = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + m4 * 4]);
-                        a0 = fmaf(l.x, x[m4 * 4 + 0], a0); a1 = fmaf(l.y, x[m4 * 4 + 1], a1);
-                        a2 = fmaf(l.z, x[m4 * 4 + 2], a2); a3 = fmaf(l.w, x[m4 * 4 + 3], a3);
-                    }
-                    x[t] = (a0 + a1) + (a2 + a3);
-                }
-                unsigned char* col = smem + OFF_TINV + (c >> 3) * CB64 + (c & 7) * 2;
-#pragma unroll
-                for (int t = 0; t < 64; ++t) *reinterpret_cast<__nv_bfloat16*>(col + t * 16) = __float2bfloat16_rn(x[t]);
-            } else if (quad < 2) {
+            tri_inverse_64<256>(lf, reinterpret_cast<float*>(smem + OFF_XINV), reinterpret_cast<float*>(smem + OFF_SCR), tid);
+            fp32_to_slab64<256>(reinterpret_cast<const float*>(smem + OFF_XINV), smem + OFF_TINV, CB64, tid);
+            if (quad < 2) {
                 if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
                 tc::fence_after_sync();
                 float g[32], gd[32];
@@ -532,15 +525,27 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     }
                 }
                 __syncthreads();
-                if (tid < 64) {   // D_{t-1} = D_t + u_t, from the carried D at the chunk end
-                    float D = sm.d_in[tid];
-                    for (int tt = 63; tt >= 0; --tt) {
-                        D += lf[tt * LF_PITCH + tid];
-                        lf[tt * LF_PITCH + tid] = D;
+                {   // D_{t-1} = D_t + u_t from the carried D at the chunk end: suffix sums, 4 segments of 16 tokens
+                    const int c = tid & 63, sg = tid >> 6;
+                    float run = 0.f;
+#pragma unroll 4
+                    for (int tt = 15; tt >= 0; --tt) {
+                        run += lf[(sg * 16 + tt) * LF_PITCH + c];
+                        lf[(sg * 16 + tt) * LF_PITCH + c] = run;
                     }
-                    // carry for the previous chunk: the exact anchor, or zero across a start flag
-                    sm.d_in[tid] = reset_here ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
+                    sm.seg[sg][c] = run;
                 }
+                __syncthreads();
+                {
+                    const int c = tid & 63, sg = tid >> 6;
+                    float off = sm.d_in[c];
+                    for (int s2 = 3; s2 > sg; --s2) off += sm.seg[s2][c];
+#pragma unroll 4
+                    for (int tt = 0; tt < 16; ++tt) lf[(sg * 16 + tt) * LF_PITCH + c] += off;
+                }
+                __syncthreads();
+                // carry for the previous chunk: the exact anchor, or zero across a start flag
+                if (tid < 64) sm.d_in[tid] = reset_here ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
                 __syncthreads();
                 if (row >= 64 && t < n) {
                     float o[32];
