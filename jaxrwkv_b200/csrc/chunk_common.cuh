@@ -40,11 +40,30 @@ __device__ __forceinline__ void slab_store(unsigned char* slab, int cb, int row,
 }
 
 
+// One warp: C(16x8) = A(16xK) B(Kx8), all fp32 row-major in shared memory, K a multiple of 8.
+__device__ __forceinline__ void tile_mma_tf32(const float* A, int lda, const float* B, int ldb, float* C, int ldc,
+                                              int K, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+    for (int k0 = 0; k0 < K; k0 += 8) {
+        const uint32_t a0 = __float_as_uint(A[g * lda + k0 + t]), a1 = __float_as_uint(A[(g + 8) * lda + k0 + t]);
+        const uint32_t a2 = __float_as_uint(A[g * lda + k0 + t + 4]), a3 = __float_as_uint(A[(g + 8) * lda + k0 + t + 4]);
+        const uint32_t b0 = __float_as_uint(B[(k0 + t) * ldb + g]), b1 = __float_as_uint(B[(k0 + t + 4) * ldb + g]);
+        asm volatile(
+            "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+    *reinterpret_cast<float2*>(&C[g * ldc + 2 * t]) = make_float2(c0, c1);
+    *reinterpret_cast<float2*>(&C[(g + 8) * ldc + 2 * t]) = make_float2(c2, c3);
+}
+
 // ---------------------------------------------------------------------------------------------
 // X = (I - L)^-1 for a 64x64 strictly lower triangular L, by all NT threads of the CTA, in fp32.
 // L and X are row-major with LF_PITCH floats per row; scr holds 32 x TRI_SCR_PITCH floats.
 // Recursive blocking: the four 16x16 diagonal blocks by forward substitution, then
-// X21 = X22 (L21 X11) for the two 32x32 blocks and once more for the whole matrix.
+// X21 = X22 (L21 X11) for the two 32x32 blocks and once more for the whole matrix (these products
+// on the warp-level tensor path in tf32).
 // Every thread must call it (it synchronises the CTA); X is complete when it returns.
 constexpr int TRI_SCR_PITCH = 36;
 constexpr int TRI_SCR_FLOATS = 32 * TRI_SCR_PITCH;
@@ -57,11 +76,19 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
         const int d = tid >> 4, c = tid & 15, o = d * 16;
         float x[16];
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-            float acc = (t == c) ? 1.f : 0.f;
+        for (int t = 0; t < 16; ++t) x[t] = 0.f;
+        // L is strictly lower and x[m] is still zero for m >= t, so every row is a full 16-long dot
+        // product: four vector loads per row that do not depend on x and can be issued ahead
 #pragma unroll
-            for (int m = 0; m < t; ++m) acc = fmaf(L[(o + t) * LF_PITCH + o + m], x[m], acc);
-            x[t] = acc;
+        for (int t = 0; t < 16; ++t) {
+            const float4* lr = reinterpret_cast<const float4*>(&L[(o + t) * LF_PITCH + o]);
+            const float4 l0 = lr[0], l1 = lr[1], l2 = lr[2], l3 = lr[3];
+            float a0 = (t == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            a0 = fmaf(l0.x, x[0], a0); a1 = fmaf(l0.y, x[1], a1); a2 = fmaf(l0.z, x[2], a2); a3 = fmaf(l0.w, x[3], a3);
+            a0 = fmaf(l1.x, x[4], a0); a1 = fmaf(l1.y, x[5], a1); a2 = fmaf(l1.z, x[6], a2); a3 = fmaf(l1.w, x[7], a3);
+            a0 = fmaf(l2.x, x[8], a0); a1 = fmaf(l2.y, x[9], a1); a2 = fmaf(l2.z, x[10], a2); a3 = fmaf(l2.w, x[11], a3);
+            a0 = fmaf(l3.x, x[12], a0); a1 = fmaf(l3.y, x[13], a1); a2 = fmaf(l3.z, x[14], a2); a3 = fmaf(l3.w, x[15], a3);
+            x[t] = (a0 + a1) + (a2 + a3);
         }
 #pragma unroll
         for (int t = 0; t < 16; ++t) X[(o + t) * LF_PITCH + o + c] = x[t];
@@ -75,46 +102,31 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
         }
     }
     __syncthreads();
-    // ---- 16 -> 32: two independent merges; W_q = L21 X11, then X21 = X22 W_q
-    for (int idx = tid; idx < 512; idx += NT) {
-        const int q = idx >> 8, i = (idx >> 4) & 15, j = idx & 15, o = q * 32;
-        float acc = 0.f;
-#pragma unroll
-        for (int m = 0; m < 16; ++m) acc = fmaf(L[(o + 16 + i) * LF_PITCH + o + m], X[(o + m) * LF_PITCH + o + j], acc);
-        scr[(q * 16 + i) * TRI_SCR_PITCH + j] = acc;
+    // ---- merges on the warp-level tensor path (m16n8k8, tf32 operands, fp32 accumulate): the result is
+    // rounded to bf16 afterwards, so tf32's 11-bit mantissa costs nothing.  One 16x8 output tile per warp.
+    const int warp = tid >> 5, lane = tid & 31;
+    // 16 -> 32: W_q = L21 X11 for q = 0,1 (two 16x16 products = four tiles), then X21 = X22 W_q
+    if (warp < 4) {
+        const int q = warp >> 1, n0 = (warp & 1) * 8, o = q * 32;
+        tile_mma_tf32(L + (o + 16) * LF_PITCH + o, LF_PITCH, X + o * LF_PITCH + o + n0, LF_PITCH,
+                      scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH, 16, lane);
     }
     __syncthreads();
-    for (int idx = tid; idx < 512; idx += NT) {
-        const int q = idx >> 8, i = (idx >> 4) & 15, j = idx & 15, o = q * 32;
-        float acc = 0.f;
-#pragma unroll
-        for (int m = 0; m < 16; ++m) acc = fmaf(X[(o + 16 + i) * LF_PITCH + o + 16 + m], scr[(q * 16 + m) * TRI_SCR_PITCH + j], acc);
-        X[(o + 16 + i) * LF_PITCH + o + j] = acc;
+    if (warp < 4) {
+        const int q = warp >> 1, n0 = (warp & 1) * 8, o = q * 32;
+        tile_mma_tf32(X + (o + 16) * LF_PITCH + o + 16, LF_PITCH, scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH,
+                      X + (o + 16) * LF_PITCH + o + n0, LF_PITCH, 16, lane);
     }
     __syncthreads();
-    // ---- 32 -> 64: W = L21 X11 (32x32x32), then X21 = X22 W ; four outputs per step and thread
-    for (int idx = tid; idx < 256; idx += NT) {
-        const int i = idx >> 3, j0 = (idx & 7) * 4;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 8
-        for (int m = 0; m < 32; ++m) {
-            const float l = L[(32 + i) * LF_PITCH + m];
-            const float4 x4 = *reinterpret_cast<const float4*>(&X[m * LF_PITCH + j0]);
-            a0 = fmaf(l, x4.x, a0); a1 = fmaf(l, x4.y, a1); a2 = fmaf(l, x4.z, a2); a3 = fmaf(l, x4.w, a3);
-        }
-        *reinterpret_cast<float4*>(&scr[i * TRI_SCR_PITCH + j0]) = make_float4(a0, a1, a2, a3);
-    }
-    __syncthreads();
-    for (int idx = tid; idx < 256; idx += NT) {
-        const int i = idx >> 3, j0 = (idx & 7) * 4;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 8
-        for (int m = 0; m < 32; ++m) {
-            const float l = X[(32 + i) * LF_PITCH + 32 + m];
-            const float4 w4 = *reinterpret_cast<const float4*>(&scr[m * TRI_SCR_PITCH + j0]);
-            a0 = fmaf(l, w4.x, a0); a1 = fmaf(l, w4.y, a1); a2 = fmaf(l, w4.z, a2); a3 = fmaf(l, w4.w, a3);
-        }
-        *reinterpret_cast<float4*>(&X[(32 + i) * LF_PITCH + j0]) = make_float4(a0, a1, a2, a3);
+    // 32 -> 64: W = L21 X11 (32x32x32 = eight tiles), then X21 = X22 W
+    static_assert(NT == 256, "the merges are laid out for eight warps");
+    {
+        const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 8;
+        tile_mma_tf32(L + (32 + m0) * LF_PITCH, LF_PITCH, X + n0, LF_PITCH, scr + m0 * TRI_SCR_PITCH + n0, TRI_SCR_PITCH,
+                      32, lane);
+        __syncthreads();
+        tile_mma_tf32(X + (32 + m0) * LF_PITCH + 32, LF_PITCH, scr + n0, TRI_SCR_PITCH, X + (32 + m0) * LF_PITCH + n0,
+                      LF_PITCH, 32, lane);
     }
     __syncthreads();
 }

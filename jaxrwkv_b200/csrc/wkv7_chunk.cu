@@ -56,6 +56,13 @@ static_assert(2 * (SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs per SM");
 
 __device__ int g_status;  // last device-side error (0 = none); see wkv7_chunk_status()
 
+#ifdef WKV_PROF
+__device__ long long g_prof[16];   // cycles per phase, summed over the chunks of CTA 0 (profiling builds only)
+#define PROF_MARK(i) do { if (bh == 0 && tid == 0) { const long long now_ = clock64(); g_prof[i] += now_ - prof_t_; prof_t_ = now_; } } while (0)
+#else
+#define PROF_MARK(i) do { } while (0)
+#endif
+
 // 256 threads: warp = (quad, hsel); quad selects the 32 TMEM lanes (tile rows) the warp may access,
 // hsel the column half it works on, so every accumulator tile is shared by two warps per row group.
 __global__ void __launch_bounds__(256, 2)
@@ -123,6 +130,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     int p = 0;
     uint32_t par = 0;
+#ifdef WKV_PROF
+    long long prof_t_ = clock64();
+#endif
     while (true) {
         // ================= boundary at position p: TMEM holds the state after token p-1 =================
         const bool want_out = (p == L);
@@ -148,6 +158,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         if (p >= Tlen) break;
 
+        PROF_MARK(0);
         // ================= extent of this chunk =================
         const int be = min(((p >> 6) + 1) << 6, Tlen);
         if (tid < 64) {
@@ -163,6 +174,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if ((mask >> 1) != 0) p1 = p + __ffsll((long long)(mask >> 1));
         if (L > p && L < p1) p1 = L;
         const int n = p1 - p;
+        PROF_MARK(1);
         // ================= stage inputs (registers), log-decay into the scan buffer =================
         uint4 raw[2][5];   // r, k, v, a, b
         float lw[2][8];    // log-decay  -exp(w)
@@ -196,6 +208,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
         __syncthreads();
+        PROF_MARK(2);
         if (tid < 128) {   // inclusive scan over tokens, two independent halves of 32 per channel
             const int j = tid & 63, half = tid >> 6;
             float run = 0.f;
@@ -215,6 +228,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             sm.lam[tid] = __expf(t2);
         }
         __syncthreads();
+        PROF_MARK(3);
         // ================= scaled operands into the slabs =================
         {
             float h1v[8], totv[8];
@@ -256,6 +270,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 slab_store(smem + OFF_V, CB64, t, jb, raw[q][2]);
             }
         }
+        PROF_MARK(4);
         // ================= entering state: bf16 copy for the products, decayed fp32 copy back to TMEM =====
         if (quad < 2) {
             float s[32];
@@ -279,6 +294,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
+        PROF_MARK(5);
         // ================= M1: pairwise products and the S0 products =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -294,6 +310,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
         tc::fence_after_sync();
+        PROF_MARK(6);
         // ================= E1: triangular masks, operands of the next products =================
         {
             const int t = row & 63;
@@ -320,6 +337,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
+        PROF_MARK(7);
         // ================= M2: G += A_ak V, Ypart += P_rk V ; meanwhile the triangular inverse =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -329,8 +347,10 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         tc::make_desc(sV + ks * 256, 128, CB64), ID_128x64_KM, true);
             tc::commit(&sm.bar[1]);
         }
+        PROF_MARK(8);
         tri_inverse_64<256>(lf, xinv, scr, tid);
         fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid);
+        PROF_MARK(9);
         if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
             tc::fence_after_sync();
@@ -343,6 +363,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
+        PROF_MARK(10);
         // ================= M3: sa = Tinv G =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -364,6 +385,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
+        PROF_MARK(11);
         // ================= M4: Y += P_rb sa ; S += sa^T B^ + V^T K^ =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -383,6 +405,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
+        PROF_MARK(12);
         if (quad >= 2) {
             const int t = row - 64;
             float yv[32];
@@ -395,6 +418,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
         tc::fence_before_sync();
+        PROF_MARK(13);
         p = p1;
         par ^= 1u;
     }
@@ -427,6 +451,15 @@ int* wkv7_chunk_status_word() {
     if (cudaGetSymbolAddress((void**)&ptr, g_status) != cudaSuccess) return nullptr;
     return ptr;
 }
+
+#ifdef WKV_PROF
+extern "C" int b200wkv_debug_prof(long long* out, int clear) {
+    long long zero[16] = {};
+    if (cudaMemcpyFromSymbol(out, g_prof, sizeof(zero)) != cudaSuccess) return -1;
+    if (clear) cudaMemcpyToSymbol(g_prof, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 // Reads and clears the device-side error word (synchronises the device; diagnostics only).
 int wkv7_chunk_status() {
