@@ -89,6 +89,52 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N,
                  void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
                  unsigned flags);
 
+/* ------------------------------------------------------- RWKV-5 / 5.2 / 6 ----
+ * jaxrwkv has no CudaRWKV class for these versions; the entry points serve the
+ * same operator seam, inner_loop(r, k, v, w, time_first, s, length, new_starts)
+ * of src/jaxrwkv/rwkv6.py:174-191, rwkv5_2.py:164-180 and rwkv5.py:161-177.
+ * The state is indexed [key][value].  `version` selects the decay operand:
+ *   6 : w is (B, T, H, N) log-decay, the kernel applies exp(w)   (rwkv6.py:176)
+ *   5 : w is (H, N) and already the decay, constant over time    (rwkv5_2.py:198; a
+ *       per-head scalar decay of RWKV-5.0 is passed broadcast to (H, N))
+ * u (time_first) is (H, N).  Backward results: dr, dk, dv, ds0 as the primals;
+ * dw is (B, T, H, N) in `dtype` for version 6 (gradient of the log-decay) and
+ * (B, H, N) fp32 per-batch partial sums for version 5; du is (B, H, N) fp32
+ * per-batch partial sums (the caller adds over B, as jaxrwkv does for RWKV-4 at
+ * rwkv4.py:351). */
+size_t b200wkv6_residual_bytes(int dtype, int B, int T, int H, int N);
+
+int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int N,
+                 const void* r, const void* k, const void* v, const void* w, const void* u,
+                 const void* s0, const uint32_t* length, const uint8_t* new_starts,
+                 void* y, void* s_out, void* residual, size_t residual_bytes, unsigned flags);
+
+int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int N,
+                 const void* r, const void* k, const void* v, const void* w, const void* u,
+                 const void* s0, const uint32_t* length, const uint8_t* new_starts,
+                 const void* dy, const void* ds_out, const void* residual, size_t residual_bytes,
+                 void* dr, void* dk, void* dv, void* dw, void* du, void* ds0, unsigned flags);
+
+/* ---------------------------------------------------------------- RWKV-4 ----
+ * Replaces the XLA custom calls "wkv4-fwd-*" / "wkv4-bwd-*" bound at
+ * src/jaxrwkv/rwkv4.py:320-321 and :347-349 (handlers WKV4FwdF32/BF16 and WKV4BwdF32/BF16, :396-400).
+ * Operand order follows those calls.  k, v, y are (B, T, C); w (already -exp(.),
+ * rwkv4.py:312) and u are (C,); states are (B, 3, C) = (aa, bb, pp); a start flag
+ * resets to (0, 0, -1e30).  y comes without the receptance factor (rwkv4.py:406).
+ * gw, gu are (B, C) fp32 per-batch partial sums (summed by the caller, rwkv4.py:351). */
+size_t b200wkv4_residual_bytes(int dtype, int B, int T, int C);
+
+int b200wkv4_fwd(void* stream, int dtype, int B, int T, int C,
+                 const void* w, const void* u, const void* k, const void* v, const void* s0,
+                 const uint32_t* length, const uint8_t* new_starts,
+                 void* s_out, void* y, void* residual, size_t residual_bytes, unsigned flags);
+
+int b200wkv4_bwd(void* stream, int dtype, int B, int T, int C,
+                 const void* w, const void* u, const void* k, const void* v, const void* gy,
+                 const void* s0, const uint32_t* length, const uint8_t* new_starts, const void* gs_new,
+                 const void* residual, size_t residual_bytes,
+                 void* gw, void* gu, void* gk, void* gv, void* gs, unsigned flags);
+
 /* Forward + backward in one call with NO residual buffer from the caller (no counterpart in
  * jaxrwkv: its kernels always take the residuals as operands).
  *

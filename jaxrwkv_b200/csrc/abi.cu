@@ -21,6 +21,21 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                    void* db, void* ds0);
 int wkv7_chunk_status();
 
+size_t wkv6_seq_residual_bytes(int B, int T, int H);
+int wkv6_seq_fwd(cudaStream_t st, int dtype, int B, int T, int H, const void* r, const void* k, const void* v,
+                 const void* w, int per_token, const void* u, const void* s0, const uint32_t* length,
+                 const uint8_t* ns, void* y, void* s_out, void* residual);
+int wkv6_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* r, const void* k, const void* v,
+                 const void* w, int per_token, const void* u, const uint32_t* length, const uint8_t* ns,
+                 const void* dy, const void* ds_out, const void* residual, void* dr, void* dk, void* dv, void* dw,
+                 void* du, void* ds0);
+size_t wkv4_residual_bytes(int B, int T, int C);
+int wkv4_fwd(cudaStream_t st, int dtype, int B, int T, int C, const void* w, const void* u, const void* k, const void* v,
+             const void* s0, const uint32_t* length, const uint8_t* ns, void* s_out, void* y, void* residual);
+int wkv4_bwd(cudaStream_t st, int dtype, int B, int T, int C, const void* w, const void* u, const void* k, const void* v,
+             const void* gy, const uint32_t* length, const uint8_t* ns, const void* gs_new, const void* residual,
+             void* gw, void* gu, void* gk, void* gv, void* gs);
+
 static int check_dims(int dtype, int B, int T, int H, int N) {
     if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
     if (B < 1 || T < 1 || H < 1 || N != kN) return B200WKV_ESHAPE;
@@ -92,6 +107,70 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void
                               residual, dw, dr, dk, dv, da, db, ds0);
     return wkv7_seq_bwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, dy, ds_out,
                         residual, dw, dr, dk, dv, da, db, ds0);
+}
+
+size_t b200wkv6_residual_bytes(int dtype, int B, int T, int H, int N) {
+    if (check_dims(dtype, B, T, H, N) != B200WKV_OK) return 0;
+    return wkv6_seq_residual_bytes(B, T, H);
+}
+
+int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int N, const void* r, const void* k,
+                 const void* v, const void* w, const void* u, const void* s0, const uint32_t* length,
+                 const uint8_t* new_starts, void* y, void* s_out, void* residual, size_t residual_bytes,
+                 unsigned flags) {
+    int st = check_dims(dtype, B, T, H, N);
+    if (st != B200WKV_OK) return st;
+    if (version != 5 && version != 6) return B200WKV_EUNSUPPORTED;
+    if (!r || !k || !v || !w || !u || !s0 || !length || !new_starts || !y || !s_out) return B200WKV_ENULL;
+    if (residual != nullptr && residual_bytes < wkv6_seq_residual_bytes(B, T, H)) return B200WKV_ERESIDUAL;
+    (void)flags;
+    return wkv6_seq_fwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, s0, length, new_starts, y,
+                        s_out, residual);
+}
+
+int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int N, const void* r, const void* k,
+                 const void* v, const void* w, const void* u, const void* s0, const uint32_t* length,
+                 const uint8_t* new_starts, const void* dy, const void* ds_out, const void* residual,
+                 size_t residual_bytes, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0, unsigned flags) {
+    int st = check_dims(dtype, B, T, H, N);
+    if (st != B200WKV_OK) return st;
+    if (version != 5 && version != 6) return B200WKV_EUNSUPPORTED;
+    if (!r || !k || !v || !w || !u || !s0 || !length || !new_starts || !residual || !dr || !dk || !dv || !dw || !du || !ds0)
+        return B200WKV_ENULL;
+    if (residual_bytes < wkv6_seq_residual_bytes(B, T, H)) return B200WKV_ERESIDUAL;
+    (void)flags;
+    return wkv6_seq_bwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy,
+                        ds_out, residual, dr, dk, dv, dw, du, ds0);
+}
+
+size_t b200wkv4_residual_bytes(int dtype, int B, int T, int C) {
+    if ((dtype != B200WKV_F32 && dtype != B200WKV_BF16) || B < 1 || T < 1 || C < 1) return 0;
+    return wkv4_residual_bytes(B, T, C);
+}
+
+int b200wkv4_fwd(void* stream, int dtype, int B, int T, int C, const void* w, const void* u, const void* k,
+                 const void* v, const void* s0, const uint32_t* length, const uint8_t* new_starts, void* s_out, void* y,
+                 void* residual, size_t residual_bytes, unsigned flags) {
+    if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
+    if (B < 1 || T < 1 || C < 1 || (long long)B * C > 2147483647LL) return B200WKV_ESHAPE;
+    if (!w || !u || !k || !v || !s0 || !length || !new_starts || !s_out || !y) return B200WKV_ENULL;
+    if (residual != nullptr && residual_bytes < wkv4_residual_bytes(B, T, C)) return B200WKV_ERESIDUAL;
+    (void)flags;
+    return wkv4_fwd((cudaStream_t)stream, dtype, B, T, C, w, u, k, v, s0, length, new_starts, s_out, y, residual);
+}
+
+int b200wkv4_bwd(void* stream, int dtype, int B, int T, int C, const void* w, const void* u, const void* k,
+                 const void* v, const void* gy, const void* s0, const uint32_t* length, const uint8_t* new_starts,
+                 const void* gs_new, const void* residual, size_t residual_bytes, void* gw, void* gu, void* gk,
+                 void* gv, void* gs, unsigned flags) {
+    if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
+    if (B < 1 || T < 1 || C < 1 || (long long)B * C > 2147483647LL) return B200WKV_ESHAPE;
+    if (!w || !u || !k || !v || !s0 || !length || !new_starts || !residual || !gw || !gu || !gk || !gv || !gs)
+        return B200WKV_ENULL;
+    if (residual_bytes < wkv4_residual_bytes(B, T, C)) return B200WKV_ERESIDUAL;
+    (void)flags;
+    return wkv4_bwd((cudaStream_t)stream, dtype, B, T, C, w, u, k, v, gy, length, new_starts, gs_new, residual, gw, gu,
+                    gk, gv, gs);
 }
 
 }  // extern "C"

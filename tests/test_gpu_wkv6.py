@@ -1,0 +1,113 @@
+"""GPU parity tests of the RWKV-5 / 5.2 / 6 kernels through the C ABI (host operator) against the
+CPU oracle, the committed reference fixtures and autograd-checked reverse loops."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from jaxrwkv_b200 import rwkv5, rwkv5_2, rwkv6, _wkv6_family as fam
+from conftest import rel_err
+from gpu_util import TOL, flags, npf
+
+pytestmark = pytest.mark.gpu
+MODS = {"6": rwkv6, "5_2": rwkv5_2, "5": rwkv5}
+NAMES = ("r", "k", "v", "w", "u", "s0")
+
+
+def case(version, B, T, H, seed, p_start=0.0, random_length=False, s0_scale=0.3, starts=None, lengths=None):
+    d = oracle.make_wkv6_inputs(B, T, H, 64, seed=seed, p_start=p_start, s0_scale=s0_scale,
+                                random_length=random_length, version=version)
+    if starts is not None:
+        ns = np.zeros((B, T), dtype=bool)
+        for i, row in enumerate(starts):
+            ns[i, list(row)] = True
+        d["new_starts"] = ns
+    if lengths is not None:
+        d["length"] = np.asarray(lengths, dtype=np.uint32)
+    return d
+
+
+def dev(d, dtype):
+    return {n: torch.tensor(d[n], dtype=torch.float32).to(dtype).cuda() for n in NAMES}
+
+
+def check(version, d, dtype, seed=0):
+    t = dev(d, dtype)
+    length, ns = flags(d)
+    leaves = [t[n].clone().requires_grad_(True) for n in NAMES]
+    s, y = MODS[version].CudaRWKV.inner_loop(*leaves[:5], leaves[5], length.cuda(), ns.cuda())
+    rounded = [t[n].double().cpu().numpy() for n in NAMES]
+    so, yo = oracle.wkv6_base_batched(*rounded, d["length"], d["new_starts"], version)
+    tol = TOL[dtype]
+    assert rel_err(npf(y), yo) < tol, ("y", rel_err(npf(y), yo))
+    for i in range(so.shape[0]):
+        assert rel_err(npf(s[i]), so[i]) < tol, ("s", i)
+    g = torch.Generator().manual_seed(seed)
+    gy = torch.randn(y.shape, generator=g).to(dtype).cuda()
+    gs = torch.randn(s.shape, generator=g).to(dtype).cuda()
+    ((y.float() * gy.float()).sum() + (s.float() * gs.float()).sum()).backward()
+    ref = oracle.wkv6_bwd_batched(*rounded, d["length"], d["new_starts"], npf(gy), npf(gs), version)
+    for n, leaf, gref in zip(("dr", "dk", "dv", "dw", "du", "ds0"), leaves, ref):
+        e = rel_err(npf(leaf.grad).reshape(gref.shape), gref)
+        assert e < tol, (n, e)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("version", ["6", "5_2", "5"])
+@pytest.mark.parametrize("T", [1, 7, 16, 17, 40, 70])
+def test_fwd_bwd_ragged(version, T, dtype):
+    rng = np.random.default_rng(T)
+    starts = [sorted(set(rng.integers(0, T, size=2).tolist())), [0], [T // 2, min(T // 2 + 1, T - 1)]]
+    lengths = [T, max(T - 3, 0), 0]
+    check(version, case(version, 3, T, 2, seed=400 + T, starts=starts, lengths=lengths), dtype)
+
+
+@pytest.mark.parametrize("version", ["6", "5_2", "5"])
+def test_reference_fixtures(golden, version):
+    g = golden(f"v{version}_resets")
+    d = {n: g["in_" + n] for n in NAMES + ("length", "new_starts")}
+    t = dev(d, torch.float32)
+    length, ns = flags(d)
+    s, y = MODS[version].CudaRWKV.inner_loop(t["r"], t["k"], t["v"], t["w"], t["u"], t["s0"], length.cuda(), ns.cuda())
+    assert rel_err(npf(y), g["base_y"]) < 1e-4 and rel_err(npf(y), g["assoc_y"]) < 1e-4
+    for i in range(s.shape[0]):
+        assert rel_err(npf(s[i]), g["base_s"][i]) < 1e-4
+        if not (int(d["length"][i]) < d["new_starts"].shape[1] and d["new_starts"][i][int(d["length"][i])]):
+            assert rel_err(npf(s[i]), g["assoc_s"][i]) < 1e-4
+
+
+def test_training_shape_v6_bf16():
+    check("6", case("6", 2, 512, 4, seed=1236, p_start=1 / 128, random_length=True, s0_scale=0.1), torch.bfloat16)
+
+
+def test_vmap_matches_batched():
+    d = case("6", 3, 33, 2, seed=5, p_start=0.1)
+    t = dev(d, torch.float32)
+    length, ns = flags(d)
+    f = rwkv6.CudaRWKV.inner_loop
+    s1, y1 = torch.vmap(f, in_dims=(0, 0, 0, 0, None, 0, 0, 0))(t["r"], t["k"], t["v"], t["w"], t["u"], t["s0"], length.cuda(), ns.cuda())
+    s2, y2 = f(t["r"], t["k"], t["v"], t["w"], t["u"], t["s0"], length.cuda(), ns.cuda())
+    assert torch.equal(y1, y2) and torch.equal(s1, s2)
+
+
+def test_config3_full_size_properties():
+    """RWKV-6 training kernel at B=16, T=4096, H=32, bf16: finite, deterministic, and exactly
+    homogeneous in (v, s0) under scaling by 2; one (batch, head) slice against the oracle."""
+    B, T, H = 16, 4096, 32
+    g = torch.Generator(device="cuda").manual_seed(1236)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    r, k, v = (rn(B, T, H, 64).bfloat16() for _ in range(3))
+    w = (-torch.exp(-0.5 + 0.5 * rn(B, T, H, 64))).bfloat16().unsqueeze(-1)
+    u = (0.1 * rn(H, 64, 1)).bfloat16()
+    s0 = (0.1 * rn(B, H, 64, 64)).bfloat16()
+    ns = torch.rand(B, T, generator=g, device="cuda") < 1 / 512
+    length = torch.full((B,), T, device="cuda")
+    s, y = rwkv6.CudaRWKV.inner_loop(r, k, v, w, u, s0, length, ns)
+    s_b, y_b = rwkv6.CudaRWKV.inner_loop(r, k, v, w, u, s0, length, ns)
+    s_2, y_2 = rwkv6.CudaRWKV.inner_loop(r, k, v * 2, w, u, s0 * 2, length, ns)
+    assert torch.isfinite(y.float()).all() and torch.equal(y, y_b) and torch.equal(s, s_b)
+    assert torch.equal(y_2, y * 2) and torch.equal(s_2, s * 2)
+    bi, hh = 3, 17
+    so, yo = oracle.wkv6_base(*[x[bi][:, hh:hh + 1].double().cpu().numpy() for x in (r, k, v, w)], u[hh:hh + 1].double().cpu().numpy(),
+                              s0[bi][hh:hh + 1].double().cpu().numpy(), T, ns[bi].cpu().numpy(), "6")
+    assert rel_err(npf(y[bi][:, hh:hh + 1]), yo) < 2e-2 and rel_err(npf(s[bi][hh:hh + 1]), so) < 2e-2
