@@ -145,4 +145,20 @@ __device__ __forceinline__ void fp32_to_slab64(const float* __restrict__ X, unsi
 
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
+// ---------------------------------------------------------------------------------------------
+// Operand walks for tcgen05.mma over the slab layout.  A descriptor is 64 bits: the low word holds
+// (address >> 4) and the leading-dimension offset, the high word the stride offset and the version,
+// so stepping along K is one 32-bit add on the low word.
+struct Op { uint32_t lo, hi, step16; };
+__device__ __forceinline__ Op make_op(uint32_t addr, uint32_t step, uint32_t lbo, uint32_t sbo) {
+    return {(addr >> 4) | ((lbo >> 4) << 16), (sbo >> 4) | (1u << 14), step >> 4};
+}
+__device__ __forceinline__ Op kmaj128(uint32_t a) { return make_op(a, 2 * CB128, CB128, 128); }   // rows = M/N, cols = K
+__device__ __forceinline__ Op kmaj64(uint32_t a) { return make_op(a, 2 * CB64, CB64, 128); }
+__device__ __forceinline__ Op mnmaj128(uint32_t a) { return make_op(a, 256, 128, CB128); }       // cols = M/N, rows = K
+__device__ __forceinline__ Op mnmaj64(uint32_t a) { return make_op(a, 256, 128, CB64); }
+__device__ __forceinline__ uint64_t op_desc(Op o, int ks) {
+    return ((uint64_t)o.hi << 32) | (uint64_t)(o.lo + (uint32_t)ks * o.step16);
+}
+
 }  // namespace b200wkv

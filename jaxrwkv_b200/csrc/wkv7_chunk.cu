@@ -54,6 +54,12 @@ constexpr int SMEM_BYTES = OFF_SMALL + (int)sizeof(Small);
 static_assert(OFF_SCR + TRI_SCR_FLOATS * 4 <= OFF_BH, "inverse work space must fit over AR+BK+S0");
 static_assert(2 * (SMEM_BYTES + 1024) <= 228 * 1024, "two CTAs per SM");
 
+// four K=16 steps (64 deep) of D (+)= A B
+__device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, bool accumulate) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) tc::mma(d, op_desc(a, ks), op_desc(b, ks), idesc, accumulate || ks > 0);
+}
+
 __device__ int g_status;  // last device-side error (0 = none); see wkv7_chunk_status()
 
 #ifdef WKV_PROF
@@ -298,14 +304,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= M1: pairwise products and the S0 products =================
         if (tid == 0) {
             tc::fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + D1, tc::make_desc(sAR + ks * 2 * CB128, CB128, 128),
-                        tc::make_desc(sBK + ks * 2 * CB128, CB128, 128), ID_128x128_KK, ks > 0);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + D2, tc::make_desc(sAR + ks * 2 * CB128, CB128, 128),
-                        tc::make_desc(sS0 + ks * 2 * CB64, CB64, 128), ID_128x64_KK, ks > 0);
+            mma_k64(tbase + D1, kmaj128(sAR), kmaj128(sBK), ID_128x128_KK, false);
+            mma_k64(tbase + D2, kmaj128(sAR), kmaj64(sS0), ID_128x64_KK, false);
             tc::commit(&sm.bar[0]);
         }
         if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
@@ -341,10 +341,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= M2: G += A_ak V, Ypart += P_rk V ; meanwhile the triangular inverse =================
         if (tid == 0) {
             tc::fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + D2, tc::make_desc(sM2A + ks * 2 * CB128, CB128, 128),
-                        tc::make_desc(sV + ks * 256, 128, CB64), ID_128x64_KM, true);
+            mma_k64(tbase + D2, kmaj128(sM2A), mnmaj64(sV), ID_128x64_KM, true);
             tc::commit(&sm.bar[1]);
         }
         PROF_MARK(8);
@@ -367,10 +364,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= M3: sa = Tinv G =================
         if (tid == 0) {
             tc::fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + D1, tc::make_desc(sTP + ks * 2 * CB128, CB128, 128),
-                        tc::make_desc(sG + ks * 256, 128, CB64), ID_128x64_KM, ks > 0);
+            mma_k64(tbase + D1, kmaj128(sTP), mnmaj64(sG), ID_128x64_KM, false);
             tc::commit(&sm.bar[2]);
         }
         if (quad < 2) {
@@ -389,18 +383,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= M4: Y += P_rb sa ; S += sa^T B^ + V^T K^ =================
         if (tid == 0) {
             tc::fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + D2, tc::make_desc(sTP + ks * 2 * CB128, CB128, 128),
-                        tc::make_desc(sSA + ks * 256, 128, CB64), ID_128x64_KM, true);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + DS, tc::make_desc(sSA + ks * 256, 128, CB64),
-                        tc::make_desc(sBH + ks * 256, 128, CB64), ID_128x64_MM, true);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-                tc::mma(tbase + DS, tc::make_desc(sV + ks * 256, 128, CB64),
-                        tc::make_desc(sKH + ks * 256, 128, CB64), ID_128x64_MM, true);
+            mma_k64(tbase + D2, kmaj128(sTP), mnmaj64(sSA), ID_128x64_KM, true);
+            mma_k64(tbase + DS, mnmaj64(sSA), mnmaj64(sBH), ID_128x64_MM, true);
+            mma_k64(tbase + DS, mnmaj64(sV), mnmaj64(sKH), ID_128x64_MM, true);
             tc::commit(&sm.bar[3]);
         }
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;

@@ -72,17 +72,17 @@ constexpr uint32_t T_DSA = 320;   // 64 : dsa
 constexpr uint32_t T_TMP = 384;   // 64 : dsa^T A~ + dY^T R~
 constexpr uint32_t T_KB = 448;    // 64 : [dK~' ; dB~']
 
-struct Op { uint32_t addr, step, lbo, sbo; };   // operand walk: descriptor of K-step ks starts at addr + ks*step
-__device__ __forceinline__ Op kmaj128(uint32_t a) { return {a, 2 * CB128, CB128, 128}; }
-__device__ __forceinline__ Op kmaj64(uint32_t a) { return {a, 2 * CB64, CB64, 128}; }
-__device__ __forceinline__ Op mnmaj128(uint32_t a) { return {a, 256, 128, CB128}; }
-__device__ __forceinline__ Op mnmaj64(uint32_t a) { return {a, 256, 128, CB64}; }
+#ifdef WKV_PROF
+__device__ long long g_prof_bwd[24];   // cycles per phase, summed over the chunks of CTA 0 (profiling builds only)
+#define PROF_MARK(i) do { if (bh == 0 && tid == 0) { const long long now_ = clock64(); g_prof_bwd[i] += now_ - prof_t_; prof_t_ = now_; } } while (0)
+#else
+#define PROF_MARK(i) do { } while (0)
+#endif
+
 // four K=16 steps (64 deep) of D (+)= A B
 __device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, bool accumulate) {
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-        tc::mma(d, tc::make_desc(a.addr + ks * a.step, a.lbo, a.sbo), tc::make_desc(b.addr + ks * b.step, b.lbo, b.sbo),
-                idesc, accumulate || ks > 0);
+    for (int ks = 0; ks < 4; ++ks) tc::mma(d, op_desc(a, ks), op_desc(b, ks), idesc, accumulate || ks > 0);
 }
 
 __global__ void __launch_bounds__(256, 1)
@@ -140,6 +140,9 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     const int tsub = tid >> 3, jb = tid & 7;   // staging unit: tokens 32q + tsub (q = 0,1), channels 8jb..8jb+7
     const int si = tid & 63, scq = tid >> 6;   // state element ownership: row si, columns 16scq..16scq+15
     uint32_t par = 0;
+#ifdef WKV_PROF
+    long long prof_t_ = clock64();
+#endif
 
     for (int blk = nBlk - 1; blk >= 0; --blk) {
         const int bs = blk * kC, be = min(bs + kC, Tlen);
@@ -174,6 +177,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     sm.d_in[tid] += acc;
                 }
             }
+            PROF_MARK(0);
             // ---------------- stage the chunk: inputs, cumulative decay ----------------
             uint4 raw[2][6];   // r, k, v, a, b, dy
             float lw[2][8];
@@ -208,6 +212,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     if (dy != nullptr) prefetch_l2(dy + gn);
                 }
             }
+            PROF_MARK(1);
             __syncthreads();
             if (tid < 128) {
                 const int j = tid & 63, half = tid >> 6;
@@ -228,6 +233,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 sm.lam[tid] = __expf(t2);
             }
             __syncthreads();
+            PROF_MARK(2);
             {
                 float h1v[8];
 #pragma unroll
@@ -263,6 +269,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     slab_store(smem + OFF_DD, CB128, t, jb, raw[q][5]);
                 }
             }
+            PROF_MARK(3);
             // ---------------- entering state (bf16) and decayed incoming state gradient (bf16) ----------------
             const float* s0src = reset_here ? nullptr : ((p % kC == 0) ? ckpt + ((size_t)bh * nBlk + p / kC) * kN * kN
                                                                         : s_at_len + st_base);
@@ -288,6 +295,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
+            PROF_MARK(4);
             // ================= R1: Gram blocks, A~ S0^T =================
             if (tid == 0) {
                 tc::fence_after_sync();
@@ -297,6 +305,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
             if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
             tc::fence_after_sync();
+            PROF_MARK(5);
             {
                 const int t = row & 63;
                 float d[64];
@@ -321,6 +330,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
+            PROF_MARK(6);
             // ================= R2: G += A_ak V ; [Gd ; dVpart] = [B~;K~] dSL^T + [P_rb|P_rk]^T dY ; inverse =================
             if (tid == 0) {
                 tc::fence_after_sync();
@@ -329,8 +339,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_GD, mnmaj64(sPRB), mnmaj128(sDD), ID_MM, true);
                 tc::commit(&sm.bar[1]);
             }
+            PROF_MARK(7);
             tri_inverse_64<256>(lf, reinterpret_cast<float*>(smem + OFF_XINV), reinterpret_cast<float*>(smem + OFF_SCR), tid);
             fp32_to_slab64<256>(reinterpret_cast<const float*>(smem + OFF_XINV), smem + OFF_TINV, CB64, tid);
+            PROF_MARK(8);
             if (quad < 2) {
                 if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
                 tc::fence_after_sync();
@@ -347,6 +359,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
+            PROF_MARK(9);
             // ================= R3: sa = T G ; dsa = T^T Gd =================
             if (tid == 0) {
                 tc::fence_after_sync();
@@ -370,6 +383,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
+            PROF_MARK(10);
             // ================= R4: dV += A_ak^T dsa ; W = [V;sa][dY;dsa]^T ; tmp = dY^T R~ + dsa^T A~ =================
             if (tid == 0) {
                 tc::fence_after_sync();
@@ -379,6 +393,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_TMP, mnmaj128(sDD + HALF), mnmaj128(sAR), ID_MM, true);
                 tc::commit(&sm.bar[3]);
             }
+            PROF_MARK(11);
             if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
             tc::fence_after_sync();
             {
@@ -442,6 +457,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
+            PROF_MARK(12);
             // ================= R5: [dK~';dB~'] and [dR~';dA~'] =================
             if (tid == 0) {
                 tc::fence_after_sync();
@@ -453,8 +469,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_G, mnmaj128(sWY), mnmaj128(sBK + HALF), ID_MM, true);
                 tc::commit(&sm.bar[4]);
             }
+            PROF_MARK(13);
             if (!tc::mbar_wait(&sm.bar[4], par)) failed = true;
             tc::fence_after_sync();
+            PROF_MARK(14);
             float p3[32];   // a_t da_t for the rows that own da
             {
                 const int t = row & 63;
@@ -508,6 +526,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         *reinterpret_cast<uint4*>(dz + g + c * 8) = pack8(&z[c * 8]);
                     }
                 }
+            PROF_MARK(15);
                 // u_t = (r dr - k dk) + (a da - b db): first the dk/dr rows write, then the db/da rows add
                 if (row < 64) {
 #pragma unroll
@@ -566,6 +585,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&o[c * 8]);
                 }
             }
+            PROF_MARK(16);
             if (reset_here) {
                 __syncthreads();
 #pragma unroll
@@ -600,6 +620,15 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 }  // namespace
 
 int* wkv7_chunk_status_word();
+
+#ifdef WKV_PROF
+extern "C" int b200wkv_debug_prof_bwd(long long* out, int clear) {
+    long long zero[24] = {};
+    if (cudaMemcpyFromSymbol(out, g_prof_bwd, sizeof(zero)) != cudaSuccess) return -1;
+    if (clear) cudaMemcpyToSymbol(g_prof_bwd, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
