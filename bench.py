@@ -53,7 +53,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -126,30 +126,15 @@ def run_reference(args):
 
 
 def make_device_inputs(torch, B, dtype, device, seed):
-    """Same distributions as oracle.inputs.make_wkv7_inputs, drawn on the device."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    shp = (B, T, H, N)
-    rn = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32)
-    r, k, v = rn(*shp), rn(*shp), rn(*shp)
-    w = -torch.nn.functional.softplus(-rn(*shp)) - 0.5
-    kk = torch.nn.functional.normalize(rn(*shp), dim=-1, eps=1e-12)
-    a = -kk
-    b = kk * torch.sigmoid(rn(*shp))
-    s0 = 0.1 * rn(B, H, N, N)
-    dy = rn(*shp)
-    ds = rn(B, H, N, N)
-    ten = {n: x.to(dtype).contiguous() for n, x in dict(r=r, w=w, k=k, v=v, a=a, b=b, s0=s0, dy=dy, ds=ds).items()}
-    ns = torch.zeros(B, T, dtype=torch.uint8, device=device)
-    ns[:, 0] = 1
-    ten["new_starts"] = ns
-    ten["length"] = torch.full((B,), T, dtype=torch.int32, device=device)
-    return ten
+    """Seeded synthetic operands at the headline shape (see jaxrwkv_b200.synthetic)."""
+    from jaxrwkv_b200.synthetic import make_wkv7_device_inputs
+    return make_wkv7_device_inputs(B, T, H, N, dtype, device, seed)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8, help="sequences per GPU")
@@ -218,42 +203,31 @@ def main():
     tokens = B * T * world
     value = tokens / (ms_step / 1e3)
 
-    # ---- end to end through the C ABI with host buffers --------------------------------------
+    # ---- end to end through the public host API: pinned host buffers in, pinned host buffers out ----
     e2e = None
     if not args.no_e2e:
+        from jaxrwkv_b200.host import wkv7_fwd_bwd_host, alloc_host_outputs
         names_in = order + ("dy", "ds")
         host_in = {n: torch.empty(x[n].shape, dtype=x[n].dtype).pin_memory() for n in names_in}
         for n in names_in:
             host_in[n].copy_(x[n])
-        dev_in = {n: torch.empty_like(x[n]) for n in names_in}
-        host_out = None
+        host_out = alloc_host_outputs(host_in)
         e_steps = max(3, min(args.steps, 5))
-
-        def e2e_step():
-            nonlocal host_out
-            for n in names_in:
-                dev_in[n].copy_(host_in[n], non_blocking=True)
-            (s, y), res = rwkv7.batched_wkv7_fwd(*[dev_in[n] for n in order], x["length"], x["new_starts"], B)
-            g = rwkv7.batched_wkv7_bwd(res, (dev_in["ds"], dev_in["dy"]), B)
-            outs = (s, y) + tuple(g)
-            if host_out is None:
-                host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-            for h, o in zip(host_out, outs):
-                h.copy_(o, non_blocking=True)
-
-        e2e_step()
+        for _ in range(2):
+            wkv7_fwd_bwd_host(host_in, x["length"], x["new_starts"], host_out)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(e_steps):
-            e2e_step()
+            wkv7_fwd_bwd_host(host_in, x["length"], x["new_starts"], host_out)   # returns after the last D2H copy
         e1.record()
         barrier()
         te_ms = max_over_ranks(e0.elapsed_time(e1), dev)
         h2d = sum(host_in[n].numel() * host_in[n].element_size() for n in names_in)
-        d2h = sum(h.numel() * h.element_size() for h in host_out)
+        d2h = sum(h.numel() * h.element_size() for h in host_out.values())
         e2e = {"value": tokens / (te_ms / e_steps / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e_steps}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e_steps,
+               "api": "jaxrwkv_b200.host.wkv7_fwd_bwd_host (batch sliced over copy-in / compute / copy-out streams)"}
 
     if rank != 0:
         if world > 1:
@@ -266,8 +240,12 @@ def main():
     peak, which = measured_peak_gbs()
     dom, dom_ms, dom_bytes = ("wkv7_bwd", bwd_ms, bwd_bytes) if bwd_ms >= fwd_ms else ("wkv7_fwd", fwd_ms, fwd_bytes)
     achieved = dom_bytes / (dom_ms / 1e3) / 1e9
+    # DRAM bytes per launch from the ncu capture at B=2 (profiles/wkv7_chunk_{fwd,bwd}_B2_T4096_H32.md:
+    # dram__bytes_read.sum + dram__bytes_write.sum), scaled by B/2 because traffic is proportional to B
+    traffic = {"wkv7_bwd": 466.9e6, "wkv7_fwd": 278.9e6}[dom] * B / 2
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": which,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                "traffic_source": "ncu capture at B=2 scaled by B/2",
                 "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                 "fwd_bwd_frac": (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms) / 1e3) / 1e9 / peak}
     cpu = None
@@ -282,6 +260,7 @@ def main():
                        "l2": "inputs (0.94 GB per step) exceed the 126 MB L2"},
             "value_per_gpu": value / world, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu,
             "clocks": clocks, "gpu_launches": 2 * args.steps * world}
+    # two launches per step and rank inside the device-timed region: wkv7_chunk_fwd_kernel, wkv7_chunk_bwd_kernel
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

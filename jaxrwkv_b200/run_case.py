@@ -1,0 +1,38 @@
+"""Run the RWKV-7 WKV forward + backward a few times on one synthetic case (for profilers and quick
+timing):  python -m jaxrwkv_b200.run_case --batch 2 --seq 4096 --heads 32 --iters 2 [--fp32]"""
+import argparse
+
+import torch
+
+from . import rwkv7
+from .synthetic import make_wkv7_device_inputs
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--fp32", action="store_true")
+    ap.add_argument("--forward-only", action="store_true")
+    a = ap.parse_args()
+    dtype = torch.float32 if a.fp32 else torch.bfloat16
+    x = make_wkv7_device_inputs(a.batch, a.seq, a.heads, 64, dtype, torch.device("cuda"), 1)
+    order = ("r", "w", "k", "v", "a", "b", "s0")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(a.iters):
+        if it == a.iters - 1:
+            e0.record()
+        (s, y), res = rwkv7.batched_wkv7_fwd(*[x[n] for n in order], x["length"], x["new_starts"], a.batch,
+                                             need_residual=not a.forward_only)
+        if not a.forward_only:
+            rwkv7.batched_wkv7_bwd(res, (x["ds"], x["dy"]), a.batch)
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"B={a.batch} T={a.seq} H={a.heads} {dtype}: last iteration {e0.elapsed_time(e1):.3f} ms, "
+          f"mean|y| {float(y.float().abs().mean()):.4f}")
+
+
+if __name__ == "__main__":
+    main()

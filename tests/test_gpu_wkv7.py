@@ -332,3 +332,23 @@ def test_chunk_bwd_full_size_properties():
         got = [g1[i][bi:bi + 1, :, hh:hh + 1] for i in range(6)] + [g1[6][bi:bi + 1, hh:hh + 1]]
         for n, a, b in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), got, ref):
             assert rel_err(npf(a), b) < TOL[torch.bfloat16], (n, bi, hh, rel_err(npf(a), b))
+
+
+def test_host_pipeline_matches_device_path():
+    """wkv7_fwd_bwd_host (pinned host tensors in and out, batch sliced over three streams) returns
+    exactly what the device-resident forward + backward return."""
+    from jaxrwkv_b200.host import wkv7_fwd_bwd_host
+    d = wkv7_case(5, 200, 2, seed=71, s0_scale=0.3, p_start=0.02, random_length=True)
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    g = torch.Generator().manual_seed(1)
+    gy = torch.randn(t["k"].shape, generator=g).bfloat16().cuda(); gs = torch.randn(t["s0"].shape, generator=g).bfloat16().cuda()
+    s, y, res = run_fwd(t, length, ns)
+    grads = rwkv7.batched_wkv7_bwd(res, (gs, gy), 5)
+    host_in = {n: t[n].cpu().pin_memory() for n in NAMES7}
+    host_in["dy"] = gy.cpu().pin_memory(); host_in["ds"] = gs.cpu().pin_memory()
+    for rows in (1, 2):
+        out = wkv7_fwd_bwd_host(host_in, length, ns, slice_rows=rows)
+        assert torch.equal(out["y"], y.cpu()) and torch.equal(out["s_out"], s.cpu())
+        for n, ref in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), grads):
+            assert torch.equal(out[n], ref.cpu()), n
