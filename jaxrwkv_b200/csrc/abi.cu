@@ -11,6 +11,9 @@ int wkv7_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w,
                  const uint8_t* ns, const void* dy, const void* ds_out, const void* residual, void* dw, void* dr,
                  void* dk, void* dv, void* da, void* db, void* ds0);
 
+int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
+              const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+              void* s_out);
 size_t wkv7_chunk_residual_bytes(int B, int T, int H);
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
@@ -83,6 +86,9 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void
     if (st != B200WKV_OK) return st;
     if (!w || !r || !k || !v || !a || !b || !s0 || !length || !new_starts || !y || !s_out) return B200WKV_ENULL;
     if (residual != nullptr && residual_bytes < b200wkv7_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
+    // one token and no residual wanted (recurrent decoding): a single pass over the state
+    if (T == 1 && residual == nullptr)
+        return wkv7_step((cudaStream_t)stream, dtype, B, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out);
     if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL))
         return wkv7_chunk_fwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
                               residual, nullptr);

@@ -407,6 +407,66 @@ wkv7_seq_bwd_kernel(int Tlen, int H, const T* __restrict__ w, const T* __restric
         store4(ds0 + tile_base + ii * kN, make_float4(dS[ii][0], dS[ii][1], dS[ii][2], dS[ii][3]));
 }
 
+// ------------------------------------------------------------------ single step -----
+// T == 1 (recurrent decoding): the whole cost is reading and writing the 64x64 state once, so the
+// kernel is a straight HBM stream.  256 threads per (batch, head): thread (i = tid/4, q = tid%4) owns
+// row i, columns 16q..16q+15.  jaxrwkv has no kernel here (it falls back to the unrolled Python loop,
+// src/jaxrwkv/rwkv7.py:469-470).
+template <typename T>
+__global__ void __launch_bounds__(256)
+wkv7_step_kernel(int H, const T* __restrict__ w, const T* __restrict__ r, const T* __restrict__ k,
+                 const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
+                 const T* __restrict__ s0, const uint32_t* __restrict__ length,
+                 const uint8_t* __restrict__ new_starts, T* __restrict__ y, T* __restrict__ s_out) {
+    const int bh = blockIdx.x, bi = bh / H;
+    const int tid = threadIdx.x, i = tid >> 2, q = tid & 3;
+    __shared__ __align__(16) float vec[6][kN];   // decay, r, k, v, a, b
+    const T* src[6] = {w, r, k, v, a, b};
+    if (tid < 96) {   // 6 streams x 16 groups of 4 elements
+        const int m = tid >> 4, lc = (tid & 15) * 4;
+        float4 x = load4(src[m] + (size_t)bh * kN + lc);
+        if (m == 0) x = make_float4(expf(-expf(x.x)), expf(-expf(x.y)), expf(-expf(x.z)), expf(-expf(x.w)));
+        *reinterpret_cast<float4*>(&vec[m][lc]) = x;
+    }
+    const size_t st = ((size_t)bh * kN + i) * kN + q * 16;
+    float S[16];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const float4 x = load4(s0 + st + g * 4);
+        S[g * 4] = x.x; S[g * 4 + 1] = x.y; S[g * 4 + 2] = x.z; S[g * 4 + 3] = x.w;
+    }
+    const bool keep_input = (length[bi] == 0);   // length == 0 returns the input state untouched
+    if (keep_input) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) store4(s_out + st + g * 4, make_float4(S[g * 4], S[g * 4 + 1], S[g * 4 + 2], S[g * 4 + 3]));
+    }
+    if (new_starts[bi]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) S[j] = 0.f;
+    }
+    __syncthreads();
+    float sa = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sa = fmaf(S[j], vec[4][q * 16 + j], sa);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+    const float vi = vec[3][i];
+    float yy = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int c = q * 16 + j;
+        S[j] = fmaf(S[j], vec[0][c], fmaf(vi, vec[2][c], sa * vec[5][c]));
+        yy = fmaf(S[j], vec[1][c], yy);
+    }
+    yy += __shfl_xor_sync(0xffffffffu, yy, 1);
+    yy += __shfl_xor_sync(0xffffffffu, yy, 2);
+    if (q == 0) y[(size_t)bh * kN + i] = from_f32<T>(yy);
+    if (!keep_input) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) store4(s_out + st + g * 4, make_float4(S[g * 4], S[g * 4 + 1], S[g * 4 + 2], S[g * 4 + 3]));
+    }
+}
+
 // ------------------------------------------------------------------ launchers -------
 size_t wkv7_seq_residual_bytes(int B, int T, int H) {
     return (size_t)B * H * ((T + kCk - 1) / kCk) * kN * kN * sizeof(float);
@@ -437,6 +497,22 @@ static int launch_bwd(cudaStream_t st, int B, int Tlen, int H, const void* w, co
                                               (const T*)a, (const T*)b, (const T*)s0, length, ns, (const T*)dy,
                                               (const T*)ds_out, (const float*)residual, (T*)dw, (T*)dr, (T*)dk,
                                               (T*)dv, (T*)da, (T*)db, (T*)ds0);
+    return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+}
+
+int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
+              const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+              void* s_out) {
+    if (dtype == B200WKV_F32)
+        wkv7_step_kernel<float><<<B * H, 256, 0, st>>>(H, (const float*)w, (const float*)r, (const float*)k, (const float*)v,
+                                                       (const float*)a, (const float*)b, (const float*)s0, length, ns,
+                                                       (float*)y, (float*)s_out);
+    else
+        wkv7_step_kernel<__nv_bfloat16><<<B * H, 256, 0, st>>>(H, (const __nv_bfloat16*)w, (const __nv_bfloat16*)r,
+                                                               (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                                                               (const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                               (const __nv_bfloat16*)s0, length, ns, (__nv_bfloat16*)y,
+                                                               (__nv_bfloat16*)s_out);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

@@ -8,6 +8,26 @@ from . import rwkv7
 from .synthetic import make_wkv7_device_inputs
 
 
+def decode(a):
+    """Recurrent decoding: one token per step, the state carried from step to step."""
+    dtype = torch.float32 if a.fp32 else torch.bfloat16
+    x = make_wkv7_device_inputs(a.batch, 1, a.heads, 64, dtype, torch.device("cuda"), 1)
+    st = x["s0"]
+    args = [x[n] for n in ("r", "w", "k", "v", "a", "b")]
+    for _ in range(3):
+        st, y = rwkv7.wkv7_step(*args, st)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        st, y = rwkv7.wkv7_step(*args, st)
+    e1.record()
+    torch.cuda.synchronize()
+    us = 1e3 * e0.elapsed_time(e1) / a.iters
+    nbytes = a.batch * a.heads * (2 * 64 * 64 + 7 * 64) * st.element_size()
+    print(f"decode B={a.batch} H={a.heads} {dtype}: {us:.1f} us/step, {a.batch / us:.2f} M tokens/s per layer, "
+          f"{nbytes / us / 1e3:.0f} GB/s of state+vector traffic")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=2)
@@ -16,7 +36,10 @@ def main():
     ap.add_argument("--iters", type=int, default=2)
     ap.add_argument("--fp32", action="store_true")
     ap.add_argument("--forward-only", action="store_true")
+    ap.add_argument("--decode", action="store_true", help="time --iters chained single-token steps (T = 1)")
     a = ap.parse_args()
+    if a.decode:
+        return decode(a)
     dtype = torch.float32 if a.fp32 else torch.bfloat16
     x = make_wkv7_device_inputs(a.batch, a.seq, a.heads, 64, dtype, torch.device("cuda"), 1)
     order = ("r", "w", "k", "v", "a", "b", "s0")

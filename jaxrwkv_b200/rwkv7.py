@@ -184,6 +184,28 @@ class _WKV7(torch.autograd.Function):
         return (new_s, out, residual), (0, 0, None)
 
 
+_STEP_FLAGS = {}
+
+
+def wkv7_step(r, w, k, v, a, b, s, new_starts=None, length=None):
+    """One decoding step without autograd bookkeeping: tensors (B, 1, H, N) or (B, H, N), state
+    (B, H, N, N).  Returns (s_out, out) with out shaped like r.  This is the T == 1 call that
+    jaxrwkv routes to the Python loop (rwkv7.py:469-470); here it is one pass over the state."""
+    shp = r.shape
+    B, H, N = shp[0], shp[-2], shp[-1]
+    flat = [x.reshape(B, 1, H, N) for x in (r, w, k, v, a, b)]
+    key = (B, r.device)
+    if key not in _STEP_FLAGS:      # default flags are constants: build them once per batch size
+        _STEP_FLAGS[key] = (torch.zeros(B, 1, dtype=torch.uint8, device=r.device),
+                            torch.ones(B, dtype=torch.int32, device=r.device))
+    if new_starts is None:
+        new_starts = _STEP_FLAGS[key][0]
+    if length is None:
+        length = _STEP_FLAGS[key][1]
+    (new_s, out), _ = batched_wkv7_fwd(*flat, s, length, new_starts.reshape(B, 1), B, need_residual=False)
+    return new_s, out.reshape(shp)
+
+
 def wkv7_cuda(r, w, k, v, a, b, s, length, new_starts):
     """Differentiable WKV-7 operator (rwkv7.py:442-446).  Tensors are (..., T, H, N) with any
     number of leading batch axes, the state (..., H, N, N); ``length`` and ``new_starts`` may

@@ -352,3 +352,27 @@ def test_host_pipeline_matches_device_path():
         assert torch.equal(out["y"], y.cpu()) and torch.equal(out["s_out"], s.cpu())
         for n, ref in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), grads):
             assert torch.equal(out[n], ref.cpu()), n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_step_kernel(dtype):
+    """T == 1 without a residual takes the single-pass step kernel: carried state, start flags on
+    some rows, length 0 on one row; then 6 chained steps against the oracle run over the 6 tokens."""
+    B, H = 5, 3
+    d = wkv7_case(B, 1, H, seed=81, s0_scale=0.7, starts=[[], [0], [], [0], []], lengths=[1, 1, 0, 0, 1])
+    t = to_dev(d, dtype)
+    length, ns = flags(d)
+    (s, y), _ = rwkv7.batched_wkv7_fwd(*[t[n] for n in NAMES7], length, ns, B, need_residual=False)
+    so, yo = oracle.wkv7_base_batched(*rounded(t), d["length"], d["new_starts"])
+    assert rel_err(npf(y), yo) < TOL[dtype]
+    for i in range(B):
+        assert rel_err(npf(s[i]), so[i]) < TOL[dtype], i
+    d = wkv7_case(2, 6, 2, seed=82, s0_scale=0.5, starts=[[3], []], lengths=[6, 6])
+    t = to_dev(d, torch.float32)
+    st = t["s0"]
+    outs = []
+    for tt in range(6):
+        st, o = rwkv7.wkv7_step(*[t[n][:, tt] for n in NAMES7[:-1]], st, new_starts=torch.tensor(d["new_starts"][:, tt]).cuda())
+        outs.append(o)
+    so, yo = oracle.wkv7_base_batched(*rounded(t), d["length"], d["new_starts"])
+    assert rel_err(npf(torch.stack(outs, 1)), yo) < 1e-4 and rel_err(npf(st), so) < 1e-4
