@@ -57,7 +57,8 @@ struct Small {
     float d_part[2][kN];   // partial column sums of the new anchor
     float seg[4][kN];      // per-16-token totals of the decay-gradient scan
     uint64_t bar[5];
-    uint32_t nsm[2];
+    uint32_t nsm[2];       // chunk starts inside the current 64-token block
+    uint32_t nsf[2];       // start flags inside the current block
     uint32_t tmem;
 };
 constexpr int SMEM_BYTES = OFF_SMALL + (int)sizeof(Small);
@@ -150,19 +151,24 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         __syncthreads();
         if (tid < 64) {
             const int pos = bs + tid;
-            const bool f = (pos < be) && (tid == 0 || new_starts[(size_t)bi * Tlen + pos] != 0 || pos == L);
-            const uint32_t m = __ballot_sync(0xffffffffu, f);
-            if (lane == 0) sm.nsm[warp] = m;
+            const bool flag = (pos < be) && (new_starts[(size_t)bi * Tlen + pos] != 0);
+            const bool f = (pos < be) && (tid == 0 || flag || pos == L);
+            const uint32_t m = __ballot_sync(0xffffffffu, f), mf = __ballot_sync(0xffffffffu, flag);
+            if (lane == 0) { sm.nsm[warp] = m; sm.nsf[warp] = mf; }
+        } else if (blk > 0 && tid < 64 + 128) {
+            // the saved state of the block processed next: one 128-byte line per thread towards L2
+            prefetch_l2(ckpt + ((size_t)bh * nBlk + blk - 1) * kN * kN + (tid - 64) * 32);
         }
         __syncthreads();
         const uint64_t cmask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
+        const uint64_t fmask = (uint64_t)sm.nsf[0] | ((uint64_t)sm.nsf[1] << 32);
         int p1 = be;
         while (p1 > bs) {
             const int rel = p1 - bs;   // 1..64
             const uint64_t below = (rel >= 64) ? cmask : (cmask & ((1ull << rel) - 1ull));
             const int p = bs + 63 - __clzll((long long)below);
             const int n = p1 - p;
-            const bool reset_here = new_starts[(size_t)bi * Tlen + p] != 0;
+            const bool reset_here = ((fmask >> (p - bs)) & 1ull) != 0;
             // ---------------- cotangent of the returned state enters at position `length` ----------------
             if (p1 == L && ds_out != nullptr) {
                 float g[16];
