@@ -240,7 +240,7 @@ def main():
     peak, which = measured_peak_gbs()
     dom, dom_ms, dom_bytes = ("wkv7_bwd", bwd_ms, bwd_bytes) if bwd_ms >= fwd_ms else ("wkv7_fwd", fwd_ms, fwd_bytes)
     achieved = dom_bytes / (dom_ms / 1e3) / 1e9
-    # DRAM bytes per launch from the ncu capture at B=2 (profiles/wkv7_chunk_{fwd,bwd}_B2_T4096_H32.md:
+    # DRAM bytes per launch from the ncu capture at B=2 (summaries of both kernels are kept under profiles/:
     # dram__bytes_read.sum + dram__bytes_write.sum), scaled by B/2 because traffic is proportional to B
     traffic = {"wkv7_bwd": 466.9e6, "wkv7_fwd": 278.9e6}[dom] * B / 2
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": which,

@@ -10,7 +10,9 @@ constexpr int CB128 = 2064;            // ... of a 128-row slab
 constexpr int SLAB64 = 8 * CB64;       // 8320
 constexpr int SLAB128 = 8 * CB128;     // 16512
 constexpr int LF_PITCH = 68;           // floats per row of fp32 matrices kept in shared memory
-constexpr float kCumFloor = -60.f;     // floor of the in-chunk cumulative log-decay (keeps 1/L finite)
+constexpr float kCumFloor = -86.56f;   // floor of the in-chunk cumulative log2-decay (= -60 in natural log; keeps 1/L finite)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
 
 // Residual written by the chunked forward for the chunked backward (all fp32):
 //   [B*H][ceil(T/64)][64][64]  state entering every 64-token block (before a start flag is applied)
@@ -141,6 +143,26 @@ __device__ __forceinline__ void fp32_to_slab64(const float* __restrict__ X, unsi
         *reinterpret_cast<float4*>(&f[4]) = *reinterpret_cast<const float4*>(&X[row * LF_PITCH + blk * 8 + 4]);
         slab_store(slab, cb, row, blk, pack8(f));
     }
+}
+
+// 2^x on the special-function unit (the cumulative decays are kept in log2 units so that no
+// multiply is needed in front of it)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// eight bf16 values (one 16-byte slab entry) times eight fp32 factors, as four packed bf16x2 products
+__device__ __forceinline__ uint4 scale8(uint4 raw, const float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    uint4 out;
+    uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 p = __hmul2(h[i], __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]));
+        o[i] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    return out;
 }
 
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }

@@ -183,7 +183,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         PROF_MARK(1);
         // ================= stage inputs (registers), log-decay into the scan buffer =================
         uint4 raw[2][5];   // r, k, v, a, b
-        float lw[2][8];    // log-decay  -exp(w)
+        float lw[2][8];    // log2 of the decay: -exp(w) * log2(e)
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const int t = q * 32 + tsub;
@@ -197,7 +197,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
                 raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
 #pragma unroll
-                for (int e = 0; e < 8; ++e) lw[q][e] = -__expf(wf[e]);
+                for (int e = 0; e < 8; ++e) lw[q][e] = -kLog2e * __expf(wf[e]);   // log2 of the decay
             } else {
 #pragma unroll
                 for (int m = 0; m < 5; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
@@ -231,7 +231,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if (tid < 64) {
             const float t2 = fmaxf(sm.h1[tid] + sm.tot[tid], kCumFloor);
             sm.tot[tid] = t2;
-            sm.lam[tid] = __expf(t2);
+            sm.lam[tid] = ex2(t2);
         }
         __syncthreads();
         PROF_MARK(3);
@@ -246,33 +246,20 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 float c[8];
                 *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8]);
                 *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8 + 4]);
-                float rf[8], kf[8], af[8], bf[8], o[8];
-                unpack8(raw[q][0], rf); unpack8(raw[q][1], kf); unpack8(raw[q][3], af); unpack8(raw[q][4], bf);
                 float eL[8], eI[8], eP[8], eE[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float cc = fmaxf(c[e] + (q == 1 ? h1v[e] : 0.f), kCumFloor);
-                    const float cp = fminf(fmaxf(cc - lw[q][e], kCumFloor), 0.f);   // cumulative log-decay before this token
-                    eL[e] = __expf(cc); eI[e] = __expf(-cc); eP[e] = __expf(cp); eE[e] = __expf(totv[e] - cc);
+                    const float cp = fminf(fmaxf(cc - lw[q][e], kCumFloor), 0.f);   // cumulative log2-decay before this token
+                    eL[e] = ex2(cc); eI[e] = ex2(-cc); eP[e] = ex2(cp); eE[e] = ex2(totv[e] - cc);
                 }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = af[e] * eP[e];
-                slab_store(smem + OFF_AR, CB128, t, jb, pack8(o));
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = rf[e] * eL[e];
-                slab_store(smem + OFF_AR, CB128, 64 + t, jb, pack8(o));
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = bf[e] * eI[e];
-                slab_store(smem + OFF_BK, CB128, t, jb, pack8(o));
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = kf[e] * eI[e];
-                slab_store(smem + OFF_BK, CB128, 64 + t, jb, pack8(o));
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = bf[e] * eE[e];
-                slab_store(smem + OFF_BH, CB64, t, jb, pack8(o));
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = kf[e] * eE[e];
-                slab_store(smem + OFF_KH, CB64, t, jb, pack8(o));
+                // raw: r, k, v, a, b
+                slab_store(smem + OFF_AR, CB128, t, jb, scale8(raw[q][3], eP));
+                slab_store(smem + OFF_AR, CB128, 64 + t, jb, scale8(raw[q][0], eL));
+                slab_store(smem + OFF_BK, CB128, t, jb, scale8(raw[q][4], eI));
+                slab_store(smem + OFF_BK, CB128, 64 + t, jb, scale8(raw[q][1], eI));
+                slab_store(smem + OFF_BH, CB64, t, jb, scale8(raw[q][4], eE));
+                slab_store(smem + OFF_KH, CB64, t, jb, scale8(raw[q][1], eE));
                 slab_store(smem + OFF_V, CB64, t, jb, raw[q][2]);
             }
         }

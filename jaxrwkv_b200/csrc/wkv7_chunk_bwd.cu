@@ -201,7 +201,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
                     raw[q][5] = (dy != nullptr) ? __ldg(reinterpret_cast<const uint4*>(dy + g)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) lw[q][e] = -__expf(wf[e]);
+                    for (int e = 0; e < 8; ++e) lw[q][e] = -kLog2e * __expf(wf[e]);   // log2 of the decay
                 } else {
 #pragma unroll
                     for (int m = 0; m < 6; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
@@ -236,7 +236,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             if (tid < 64) {
                 const float t2 = fmaxf(sm.h1[tid] + sm.tot[tid], kCumFloor);
                 sm.tot[tid] = t2;
-                sm.lam[tid] = __expf(t2);
+                sm.lam[tid] = ex2(t2);
             }
             __syncthreads();
             PROF_MARK(2);
@@ -250,27 +250,18 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     float c[8];
                     *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8]);
                     *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8 + 4]);
-                    float rf[8], kf[8], af[8], bf[8], o[8];
-                    unpack8(raw[q][0], rf); unpack8(raw[q][1], kf); unpack8(raw[q][3], af); unpack8(raw[q][4], bf);
                     float eL[8], eI[8], eP[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const float cc = fmaxf(c[e] + (q == 1 ? h1v[e] : 0.f), kCumFloor);
                         const float cp = fminf(fmaxf(cc - lw[q][e], kCumFloor), 0.f);
-                        eL[e] = __expf(cc); eI[e] = __expf(-cc); eP[e] = __expf(cp);
+                        eL[e] = ex2(cc); eI[e] = ex2(-cc); eP[e] = ex2(cp);
                     }
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] = af[e] * eP[e];
-                    slab_store(smem + OFF_AR, CB128, t, jb, pack8(o));
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] = rf[e] * eL[e];
-                    slab_store(smem + OFF_AR, CB128, 64 + t, jb, pack8(o));
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] = bf[e] * eI[e];
-                    slab_store(smem + OFF_BK, CB128, t, jb, pack8(o));
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] = kf[e] * eI[e];
-                    slab_store(smem + OFF_BK, CB128, 64 + t, jb, pack8(o));
+                    // raw: r, k, v, a, b, dy
+                    slab_store(smem + OFF_AR, CB128, t, jb, scale8(raw[q][3], eP));
+                    slab_store(smem + OFF_AR, CB128, 64 + t, jb, scale8(raw[q][0], eL));
+                    slab_store(smem + OFF_BK, CB128, t, jb, scale8(raw[q][4], eI));
+                    slab_store(smem + OFF_BK, CB128, 64 + t, jb, scale8(raw[q][1], eI));
                     slab_store(smem + OFF_VSA, CB128, t, jb, raw[q][2]);
                     slab_store(smem + OFF_DD, CB128, t, jb, raw[q][5]);
                 }
@@ -509,16 +500,16 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         const int c = hsel * 32 + e;
                         const float cc = fmaxf(cr[e] + (t >= 32 ? sm.h1[c] : 0.f), kCumFloor);
                         lwt[e] = cr[e] - cp[e];
-                        const float eI = __expf(-cc);
+                        const float eI = ex2(-cc);
                         if (row < 64) {          // dk, dr ; u = r dr - k dk
                             u[e] = s1[e] * z[e] - s2[e] * x[e];
                             x[e] *= eI;
-                            z[e] *= __expf(cc);
+                            z[e] *= ex2(cc);
                         } else {                 // db, da ; u = a da - b db
                             p3[e] = s1[e] * z[e];
                             u[e] = p3[e] - s2[e] * x[e];
                             x[e] *= eI;
-                            z[e] *= __expf(fminf(fmaxf(cc - lwt[e], kCumFloor), 0.f));
+                            z[e] *= ex2(fminf(fmaxf(cc - lwt[e], kCumFloor), 0.f));
                         }
                     }
                 }
@@ -577,10 +568,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
                     for (int c4 = 0; c4 < 8; ++c4) {
                         const float4 d4 = *reinterpret_cast<const float4*>(&lf[t * LF_PITCH + hsel * 32 + c4 * 4]);
-                        o[c4 * 4 + 0] = (d4.x - p3[c4 * 4 + 0]) * lwt[c4 * 4 + 0];
-                        o[c4 * 4 + 1] = (d4.y - p3[c4 * 4 + 1]) * lwt[c4 * 4 + 1];
-                        o[c4 * 4 + 2] = (d4.z - p3[c4 * 4 + 2]) * lwt[c4 * 4 + 2];
-                        o[c4 * 4 + 3] = (d4.w - p3[c4 * 4 + 3]) * lwt[c4 * 4 + 3];
+                        o[c4 * 4 + 0] = (d4.x - p3[c4 * 4 + 0]) * (kLn2 * lwt[c4 * 4 + 0]);
+                        o[c4 * 4 + 1] = (d4.y - p3[c4 * 4 + 1]) * (kLn2 * lwt[c4 * 4 + 1]);
+                        o[c4 * 4 + 2] = (d4.z - p3[c4 * 4 + 2]) * (kLn2 * lwt[c4 * 4 + 2]);
+                        o[c4 * 4 + 3] = (d4.w - p3[c4 * 4 + 3]) * (kLn2 * lwt[c4 * 4 + 3]);
                     }
                     if (reset_here && t == 0) {   // the state entering a start token is zero: no decay gradient
 #pragma unroll
