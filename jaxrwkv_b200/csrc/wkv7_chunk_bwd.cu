@@ -145,9 +145,17 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     long long prof_t_ = clock64();
 #endif
 
-    for (int blk = nBlk - 1; blk >= 0; --blk) {
-        const int bs = blk * kC, be = min(bs + kC, Tlen);
-        // chunk starts inside this block: its first token, every start flag, and `length`
+    // ---- chunk schedule, walked in reverse.  The extent and the global loads of the next chunk are
+    // issued while the tail of the current one (decay-gradient scan) still runs.
+    int blk = nBlk - 1, bs = 0, be = 0, p1 = 0, p = 0, n = 0;
+    uint64_t cmask = 0, fmask = 0;
+    bool reset_here = false;
+    uint4 raw[2][6];   // r, k, v, a, b, dy
+    uint4 wraw[2];     // raw log-log decay
+    auto plan_block = [&](int b) {
+        // chunk starts inside block b: its first token, every start flag, and `length`
+        bs = b * kC;
+        be = min(bs + kC, Tlen);
         __syncthreads();
         if (tid < 64) {
             const int pos = bs + tid;
@@ -155,20 +163,54 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             const bool f = (pos < be) && (tid == 0 || flag || pos == L);
             const uint32_t m = __ballot_sync(0xffffffffu, f), mf = __ballot_sync(0xffffffffu, flag);
             if (lane == 0) { sm.nsm[warp] = m; sm.nsf[warp] = mf; }
-        } else if (blk > 0 && tid < 64 + 128) {
-            // the saved state of the block processed next: one 128-byte line per thread towards L2
-            prefetch_l2(ckpt + ((size_t)bh * nBlk + blk - 1) * kN * kN + (tid - 64) * 32);
+        } else if (b > 0 && tid < 64 + 128) {
+            // the saved state of the block processed after this one: one 128-byte line per thread towards L2
+            prefetch_l2(ckpt + ((size_t)bh * nBlk + b - 1) * kN * kN + (tid - 64) * 32);
         }
         __syncthreads();
-        const uint64_t cmask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
-        const uint64_t fmask = (uint64_t)sm.nsf[0] | ((uint64_t)sm.nsf[1] << 32);
-        int p1 = be;
-        while (p1 > bs) {
-            const int rel = p1 - bs;   // 1..64
-            const uint64_t below = (rel >= 64) ? cmask : (cmask & ((1ull << rel) - 1ull));
-            const int p = bs + 63 - __clzll((long long)below);
-            const int n = p1 - p;
-            const bool reset_here = ((fmask >> (p - bs)) & 1ull) != 0;
+        cmask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
+        fmask = (uint64_t)sm.nsf[0] | ((uint64_t)sm.nsf[1] << 32);
+    };
+    auto plan_chunk = [&](int end) {   // the chunk [p, end) of the current block, bs < end <= be
+        const int rel = end - bs;      // 1..64
+        const uint64_t below = (rel >= 64) ? cmask : (cmask & ((1ull << rel) - 1ull));
+        p = bs + 63 - __clzll((long long)below);
+        n = end - p;
+        reset_here = ((fmask >> (p - bs)) & 1ull) != 0;
+    };
+    auto issue_loads = [&]() {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int t = q * 32 + tsub;
+            if (t < n) {
+                const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
+                wraw[q] = __ldg(reinterpret_cast<const uint4*>(w + g));
+                raw[q][0] = __ldg(reinterpret_cast<const uint4*>(r + g));
+                raw[q][1] = __ldg(reinterpret_cast<const uint4*>(k + g));
+                raw[q][2] = __ldg(reinterpret_cast<const uint4*>(v + g));
+                raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
+                raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
+                raw[q][5] = (dy != nullptr) ? __ldg(reinterpret_cast<const uint4*>(dy + g)) : make_uint4(0, 0, 0, 0);
+            } else {
+                wraw[q] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int m = 0; m < 6; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
+            }
+            // pull the lines of the 64 tokens in front of this chunk (processed after it) towards L2
+            if (jb == 0 && p - kC + t >= 0) {
+                const size_t gn = seq_base + (size_t)(p - kC + t) * tok_stride;
+                prefetch_l2(w + gn); prefetch_l2(r + gn); prefetch_l2(k + gn); prefetch_l2(v + gn);
+                prefetch_l2(a + gn); prefetch_l2(b + gn);
+                if (dy != nullptr) prefetch_l2(dy + gn);
+            }
+        }
+    };
+    plan_block(blk);
+    p1 = be;
+    plan_chunk(p1);
+    while (true) {
+        {
+            issue_loads();
             // ---------------- cotangent of the returned state enters at position `length` ----------------
             if (p1 == L && ds_out != nullptr) {
                 float g[16];
@@ -184,39 +226,17 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
             }
             PROF_MARK(0);
-            // ---------------- stage the chunk: inputs, cumulative decay ----------------
-            uint4 raw[2][6];   // r, k, v, a, b, dy
+            // ---------------- cumulative decay of the chunk ----------------
             float lw[2][8];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int t = q * 32 + tsub;
-                if (t < n) {
-                    const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
-                    float wf[8];
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(w + g)), wf);
-                    raw[q][0] = __ldg(reinterpret_cast<const uint4*>(r + g));
-                    raw[q][1] = __ldg(reinterpret_cast<const uint4*>(k + g));
-                    raw[q][2] = __ldg(reinterpret_cast<const uint4*>(v + g));
-                    raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
-                    raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
-                    raw[q][5] = (dy != nullptr) ? __ldg(reinterpret_cast<const uint4*>(dy + g)) : make_uint4(0, 0, 0, 0);
+                float wf[8];
+                unpack8(wraw[q], wf);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) lw[q][e] = -kLog2e * __expf(wf[e]);   // log2 of the decay
-                } else {
-#pragma unroll
-                    for (int m = 0; m < 6; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) lw[q][e] = 0.f;
-                }
+                for (int e = 0; e < 8; ++e) lw[q][e] = (t < n) ? -kLog2e * __expf(wf[e]) : 0.f;   // log2 of the decay
                 *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
                 *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
-                // pull the lines of the 64 tokens in front of this chunk (processed next) towards L2
-                if (jb == 0 && p - kC + t >= 0) {
-                    const size_t gn = seq_base + (size_t)(p - kC + t) * tok_stride;
-                    prefetch_l2(w + gn); prefetch_l2(r + gn); prefetch_l2(k + gn); prefetch_l2(v + gn);
-                    prefetch_l2(a + gn); prefetch_l2(b + gn);
-                    if (dy != nullptr) prefetch_l2(dy + gn);
-                }
             }
             PROF_MARK(1);
             __syncthreads();
@@ -467,6 +487,41 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 tc::commit(&sm.bar[4]);
             }
             PROF_MARK(13);
+            // everything of the epilogue that does not depend on the products runs while they execute:
+            // decay factors of this row and the operand rows it pairs with (kept packed)
+            float fx[32], fz[32], lwt[32];
+            uint4 s1raw[4], s2raw[4];
+            int cur_p, cur_n;
+            bool cur_reset, has_next;
+            {
+                const int t = row & 63;
+                const unsigned char* slab1 = smem + OFF_AR + ((row < 64) ? (64 + t) * 16 : t * 16);   // R~ / A~
+                const unsigned char* slab2 = smem + OFF_BK + ((row < 64) ? (64 + t) * 16 : t * 16);   // K~ / B~
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    s1raw[c8] = *reinterpret_cast<const uint4*>(slab1 + (hsel * 4 + c8) * CB128);
+                    s2raw[c8] = *reinterpret_cast<const uint4*>(slab2 + (hsel * 4 + c8) * CB128);
+                }
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const int c = hsel * 32 + c4 * 4;
+                    const float4 cr4 = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + c]);
+                    const float4 cp4 = (t & 31) ? *reinterpret_cast<const float4*>(&cum[(t - 1) * LF_PITCH + c])
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 h4 = (t >= 32) ? *reinterpret_cast<const float4*>(&sm.h1[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float cr[4] = {cr4.x, cr4.y, cr4.z, cr4.w}, cp[4] = {cp4.x, cp4.y, cp4.z, cp4.w};
+                    const float hh[4] = {h4.x, h4.y, h4.z, h4.w};
+#pragma unroll
+                    for (int e4 = 0; e4 < 4; ++e4) {
+                        const int e = c4 * 4 + e4;
+                        const float cc = fmaxf(cr[e4] + hh[e4], kCumFloor);
+                        lwt[e] = cr[e4] - cp[e4];
+                        fx[e] = ex2(-cc);                                                     // dk, db: 1 / L_t
+                        fz[e] = (row < 64) ? ex2(cc)                                            // dr: L_t
+                                           : ex2(fminf(fmaxf(cc - lwt[e], kCumFloor), 0.f));    // da: L_{t-1}
+                    }
+                }
+            }
             if (!tc::mbar_wait(&sm.bar[4], par)) failed = true;
             tc::fence_after_sync();
             PROF_MARK(14);
@@ -477,40 +532,23 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 tc::tmem_ld32(lane_addr + T_KB + hsel * 32, x);
                 tc::tmem_ld32(lane_addr + T_G + hsel * 32, z);
                 tc::tmem_wait_ld();
-                float u[32], lwt[32];
-                {
-                    // this row's cumulative log-decay, the previous row's, and the two operand rows it pairs with
-                    float cr[32], cp[32], s1[32], s2[32];
-                    const unsigned char* slab1 = smem + OFF_AR + ((row < 64) ? (64 + t) * 16 : t * 16);   // R~ / A~
-                    const unsigned char* slab2 = smem + OFF_BK + ((row < 64) ? (64 + t) * 16 : t * 16);   // K~ / B~
+                float u[32];
 #pragma unroll
-                    for (int c4 = 0; c4 < 8; ++c4) {
-                        const int c = hsel * 32 + c4 * 4;
-                        *reinterpret_cast<float4*>(&cr[c4 * 4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + c]);
-                        *reinterpret_cast<float4*>(&cp[c4 * 4]) = (t & 31) ? *reinterpret_cast<const float4*>(&cum[(t - 1) * LF_PITCH + c])
-                                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    float s1[8], s2[8];
+                    unpack8(s1raw[c8], s1);
+                    unpack8(s2raw[c8], s2);
 #pragma unroll
-                    for (int c8 = 0; c8 < 4; ++c8) {
-                        unpack8(*reinterpret_cast<const uint4*>(slab1 + (hsel * 4 + c8) * CB128), &s1[c8 * 8]);
-                        unpack8(*reinterpret_cast<const uint4*>(slab2 + (hsel * 4 + c8) * CB128), &s2[c8 * 8]);
-                    }
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int c = hsel * 32 + e;
-                        const float cc = fmaxf(cr[e] + (t >= 32 ? sm.h1[c] : 0.f), kCumFloor);
-                        lwt[e] = cr[e] - cp[e];
-                        const float eI = ex2(-cc);
+                    for (int e8 = 0; e8 < 8; ++e8) {
+                        const int e = c8 * 8 + e8;
                         if (row < 64) {          // dk, dr ; u = r dr - k dk
-                            u[e] = s1[e] * z[e] - s2[e] * x[e];
-                            x[e] *= eI;
-                            z[e] *= ex2(cc);
+                            u[e] = s1[e8] * z[e] - s2[e8] * x[e];
                         } else {                 // db, da ; u = a da - b db
-                            p3[e] = s1[e] * z[e];
-                            u[e] = p3[e] - s2[e] * x[e];
-                            x[e] *= eI;
-                            z[e] *= ex2(fminf(fmaxf(cc - lwt[e], kCumFloor), 0.f));
+                            p3[e] = s1[e8] * z[e];
+                            u[e] = p3[e] - s2[e8] * x[e];
                         }
+                        x[e] *= fx[e];
+                        z[e] *= fz[e];
                     }
                 }
                 if (t < n) {
@@ -522,6 +560,13 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         *reinterpret_cast<uint4*>(dx + g + c * 8) = pack8(&x[c * 8]);
                         *reinterpret_cast<uint4*>(dz + g + c * 8) = pack8(&z[c * 8]);
                     }
+                }
+                // ---------------- plan the next chunk and issue its loads; the rest of this chunk is the scan
+                cur_p = p; cur_n = n; cur_reset = reset_here;
+                has_next = cur_p > 0;
+                if (has_next) {
+                    if (cur_p == bs) plan_block(--blk);
+                    plan_chunk(cur_p);
                 }
             PROF_MARK(15);
                 // u_t = (r dr - k dk) + (a da - b db): first the dk/dr rows write, then the db/da rows add
@@ -561,9 +606,9 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 __syncthreads();
                 // carry for the previous chunk: the exact anchor, or zero across a start flag
-                if (tid < 64) sm.d_in[tid] = reset_here ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
+                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
                 __syncthreads();
-                if (row >= 64 && t < n) {
+                if (row >= 64 && t < cur_n) {
                     float o[32];
 #pragma unroll
                     for (int c4 = 0; c4 < 8; ++c4) {
@@ -573,24 +618,25 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         o[c4 * 4 + 2] = (d4.z - p3[c4 * 4 + 2]) * (kLn2 * lwt[c4 * 4 + 2]);
                         o[c4 * 4 + 3] = (d4.w - p3[c4 * 4 + 3]) * (kLn2 * lwt[c4 * 4 + 3]);
                     }
-                    if (reset_here && t == 0) {   // the state entering a start token is zero: no decay gradient
+                    if (cur_reset && t == 0) {   // the state entering a start token is zero: no decay gradient
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] = 0.f;
                     }
-                    __nv_bfloat16* dst = dw + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+                    __nv_bfloat16* dst = dw + seq_base + (size_t)(cur_p + t) * tok_stride + hsel * 32;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&o[c * 8]);
                 }
             }
             PROF_MARK(16);
-            if (reset_here) {
+            if (cur_reset) {
                 __syncthreads();
 #pragma unroll
                 for (int e = 0; e < 16; ++e) dsf[si * LF_PITCH + scq * 16 + e] = 0.f;
             }
             tc::fence_before_sync();
-            p1 = p;
             par ^= 1u;
+            if (!has_next) break;
+            p1 = cur_p;
         }
     }
     __syncthreads();
