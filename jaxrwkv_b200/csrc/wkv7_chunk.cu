@@ -136,6 +136,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     int p = 0;
     uint32_t par = 0;
+    uint8_t flag_ahead = (tid < 64 && tid < Tlen) ? new_starts[(size_t)bi * Tlen + tid] : 0;
 #ifdef WKV_PROF
     long long prof_t_ = clock64();
 #endif
@@ -168,8 +169,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= extent of this chunk =================
         const int be = min(((p >> 6) + 1) << 6, Tlen);
         if (tid < 64) {
-            const int pos = p + tid;
-            const bool f = (pos < be) && (new_starts[(size_t)bi * Tlen + pos] != 0);
+            // the flag byte of position p + tid was requested while the previous chunk's products ran
+            const bool f = (p + tid < be) && (flag_ahead != 0);
             const uint32_t m = __ballot_sync(0xffffffffu, f);
             if (lane == 0) sm.nsm[warp] = m;
         }
@@ -375,6 +376,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             mma_k64(tbase + DS, mnmaj64(sV), mnmaj64(sKH), ID_128x64_MM, true);
             tc::commit(&sm.bar[3]);
         }
+        if (tid < 64) flag_ahead = (p1 + tid < Tlen) ? new_starts[(size_t)bi * Tlen + p1 + tid] : 0;   // next chunk's start flags
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
         PROF_MARK(12);
