@@ -46,6 +46,11 @@ extern "C" {
 const char* b200wkv_strerror(int status);
 /* ABI version of the loaded library (incremented on incompatible change). */
 int b200wkv_abi_version(void);
+/* Diagnostics: reads and clears the device-side error word of the current device (0 = none).
+ * The tensor-core kernels bound every wait on an asynchronous product; a wait that runs out is
+ * recorded there (1 = forward, 2 = backward) and the kernel still terminates.  This call
+ * synchronises the device, so it is not for the hot path.  Returns -1 if the CUDA runtime fails. */
+int b200wkv_device_status(void);
 
 /* ---------------------------------------------------------------- RWKV-7 ----
  * Replaces the XLA custom calls "wkv7-fwd-{fp32,bf16}" / "wkv7-bwd-{fp32,bf16}"

@@ -17,6 +17,7 @@ _U = ctypes.c_uint
 PROTOTYPES = {
     "b200wkv_strerror": (ctypes.c_char_p, [_I]),
     "b200wkv_abi_version": (_I, []),
+    "b200wkv_device_status": (_I, []),
     "b200wkv7_residual_bytes": (_SZ, [_I, _I, _I, _I, _I]),
     "b200wkv7_fwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ, _U]),
     "b200wkv7_bwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ] + [_P] * 7 + [_U]),

@@ -68,6 +68,8 @@ const char* b200wkv_strerror(int status) {
 
 int b200wkv_abi_version(void) { return 1; }
 
+int b200wkv_device_status(void) { return wkv7_chunk_status(); }
+
 size_t b200wkv7_residual_bytes(int dtype, int B, int T, int H, int N) {
     if (check_dims(dtype, B, T, H, N) != B200WKV_OK) return 0;
     // fp32 uses the sequential kernels (a state every 16 tokens); bf16 uses the chunked tensor-core

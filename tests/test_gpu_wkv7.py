@@ -376,3 +376,9 @@ def test_decode_step_kernel(dtype):
         outs.append(o)
     so, yo = oracle.wkv7_base_batched(*rounded(t), d["length"], d["new_starts"])
     assert rel_err(npf(torch.stack(outs, 1)), yo) < 1e-4 and rel_err(npf(st), so) < 1e-4
+
+
+def test_no_bounded_wait_ran_out_during_the_suite():
+    """Every mbarrier wait in the tensor-core kernels is bounded and records a failure in a device
+    word; after the tensor-core tests above that word must still be clear."""
+    assert _lib.load().b200wkv_device_status() == 0
