@@ -140,6 +140,27 @@ int b200wkv4_bwd(void* stream, int dtype, int B, int T, int C,
                  const void* residual, size_t residual_bytes,
                  void* gw, void* gu, void* gk, void* gv, void* gs, unsigned flags);
 
+/* ------------------------------------------------------------ token shift ----
+ * The per-token state the callers of the operator keep next to it: the shift by one token with
+ * the carried last row and start flags (src/jaxrwkv/rwkv7.py:226-235, :254 for time mixing and
+ * :192-197 for channel mixing), fused with the M interpolations x + (shifted - x) * mix_m.
+ * x (B, T, D), prev (B, D), mix (M, D) with M <= 8, D a multiple of 4; out (M, B, T, D);
+ * state_out (B, D) = x[(length - 1) mod T] (the reference indexes x[length-1], so length 0 wraps
+ * to the last row).  Backward: gout (M, B, T, D) and gstate (B, D, may be NULL) in; gx, gprev as
+ * the primals; gmix (B, ceil(T / B200WKV_SHIFT_TILE), M, D) fp32 partial sums, one per batch row
+ * and tile of tokens (the caller adds over the first two axes: deterministic, no atomics). */
+#define B200WKV_SHIFT_TILE 64
+int b200wkv_token_shift_fwd(void* stream, int dtype, int B, int T, int D, int M,
+                            const void* x, const void* prev, const void* mix,
+                            const uint32_t* length, const uint8_t* new_starts,
+                            void* out, void* state_out);
+
+int b200wkv_token_shift_bwd(void* stream, int dtype, int B, int T, int D, int M,
+                            const void* x, const void* prev, const void* mix,
+                            const uint32_t* length, const uint8_t* new_starts,
+                            const void* gout, const void* gstate,
+                            void* gx, void* gprev, void* gmix);
+
 /* Forward + backward in one call with NO residual buffer from the caller (no counterpart in
  * jaxrwkv: its kernels always take the residuals as operands).
  *

@@ -27,6 +27,8 @@ PROTOTYPES = {
     "b200wkv4_residual_bytes": (_SZ, [_I, _I, _I, _I]),
     "b200wkv4_fwd": (_I, [_P, _I, _I, _I, _I] + [_P] * 7 + [_P, _P, _P, _SZ, _U]),
     "b200wkv4_bwd": (_I, [_P, _I, _I, _I, _I] + [_P] * 9 + [_P, _SZ] + [_P] * 5 + [_U]),
+    "b200wkv_token_shift_fwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 7),
+    "b200wkv_token_shift_bwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 10),
     "b200wkv7_static_scratch_bytes": (_SZ, []),
     "b200wkv7_fwd_bwd_static": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P] + [_P, _P] + [_P] * 7 + [_U]),
 }

@@ -39,6 +39,12 @@ int wkv4_bwd(cudaStream_t st, int dtype, int B, int T, int C, const void* w, con
              const void* gy, const uint32_t* length, const uint8_t* ns, const void* gs_new, const void* residual,
              void* gw, void* gu, void* gk, void* gv, void* gs);
 
+int token_shift_fwd(cudaStream_t st, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
+                    const void* mix, const uint32_t* length, const uint8_t* ns, void* out, void* state_out);
+int token_shift_bwd(cudaStream_t st, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
+                    const void* mix, const uint32_t* length, const uint8_t* ns, const void* gout, const void* gstate,
+                    void* gx, void* gprev, void* gmix);
+
 static int check_dims(int dtype, int B, int T, int H, int N) {
     if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
     if (B < 1 || T < 1 || H < 1 || N != kN) return B200WKV_ESHAPE;
@@ -179,6 +185,31 @@ int b200wkv4_bwd(void* stream, int dtype, int B, int T, int C, const void* w, co
     (void)flags;
     return wkv4_bwd((cudaStream_t)stream, dtype, B, T, C, w, u, k, v, gy, length, new_starts, gs_new, residual, gw, gu,
                     gk, gv, gs);
+}
+
+static int check_shift(int dtype, int B, int T, int D, int M) {
+    if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
+    if (B < 1 || T < 1 || D < 4 || (D % 4) != 0 || M < 1 || M > 8 || (long long)B * T > 2147483647LL || B > 65535) return B200WKV_ESHAPE;
+    return B200WKV_OK;
+}
+
+int b200wkv_token_shift_fwd(void* stream, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
+                            const void* mix, const uint32_t* length, const uint8_t* new_starts, void* out,
+                            void* state_out) {
+    int st = check_shift(dtype, B, T, D, M);
+    if (st != B200WKV_OK) return st;
+    if (!x || !prev || !mix || !length || !new_starts || !out || !state_out) return B200WKV_ENULL;
+    return token_shift_fwd((cudaStream_t)stream, dtype, B, T, D, M, x, prev, mix, length, new_starts, out, state_out);
+}
+
+int b200wkv_token_shift_bwd(void* stream, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
+                            const void* mix, const uint32_t* length, const uint8_t* new_starts, const void* gout,
+                            const void* gstate, void* gx, void* gprev, void* gmix) {
+    int st = check_shift(dtype, B, T, D, M);
+    if (st != B200WKV_OK) return st;
+    if (!x || !prev || !mix || !length || !new_starts || !gout || !gx || !gprev || !gmix) return B200WKV_ENULL;
+    return token_shift_bwd((cudaStream_t)stream, dtype, B, T, D, M, x, prev, mix, length, new_starts, gout, gstate, gx,
+                           gprev, gmix);
 }
 
 }  // extern "C"

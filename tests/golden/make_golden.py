@@ -87,6 +87,34 @@ def run_v4(mod, d):
     return out
 
 
+def run_shift(mod, name, seed):
+    """Token shift of RWKV-7 through the reference's own ``channel_mixing_seq`` (rwkv7.py:192-197).
+
+    With identity key/value matrices the function returns ``relu(xk)**2``; inputs are positive and the
+    mix lies in [0, 1], so ``xk >= 0`` and its square root is the shifted-and-mixed input itself.
+    """
+    import jax.numpy as jnp
+    rng = np.random.default_rng(seed)
+    B, T, D = 3, 19, 16
+    x = rng.uniform(0.1, 2.0, (B, T, D)).astype(np.float32)
+    prev = rng.uniform(0.1, 2.0, (B, D)).astype(np.float32)
+    mix = rng.uniform(0.0, 1.0, (1, D)).astype(np.float32)
+    ns = np.zeros((B, T), bool)
+    ns[0, [0, 7]] = True; ns[1, [5, 6, 18]] = True
+    length = np.asarray([19, 12, 0], dtype=np.uint32)
+    eye = jnp.asarray(np.eye(D))
+    xk, last = [], []
+    for i in range(B):
+        ffn = {"x_k": jnp.asarray(mix[0].astype(np.float64)), "key": {"weight": eye}, "value": {"weight": eye}}
+        out, row = mod.BaseRWKV.channel_mixing_seq(jnp.asarray(x[i].astype(np.float64)), jnp.asarray(prev[i:i + 1].astype(np.float64)),
+                                                   ffn, int(length[i]), jnp.asarray(ns[i]))
+        xk.append(np.sqrt(np.asarray(out))); last.append(np.asarray(row))
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, in_x=x, in_prev=prev, in_mix=mix, in_new_starts=ns, in_length=length,
+                        xk=np.stack(xk), last=np.stack(last))
+    print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def save(name, d, res):
     base_s, base_y = res["BaseRWKV"]
     scan_s, scan_y = res["ScanRWKV"]
@@ -127,6 +155,8 @@ def main():
     d = make_wkv7_inputs(2, 21, 3, 8, seed=103, s0_scale=1.0)         # small head size, oracle-only
     set_starts(d, [(0, 7), (3, 20)], [21, 13])
     save("v7_small", d, run_v7(mods["7"], d))
+
+    run_shift(mods["7"], "v7_token_shift", 104)
 
     # RWKV-6 / 5.2 / 5 -------------------------------------------------------------------
     for version, seed in (("6", 201), ("5_2", 202), ("5", 203)):

@@ -127,3 +127,14 @@ def test_torch_restatements_match_numpy():
     s_np, y_np = oracle.wkv4_base(d4["r"][0], d4["k"][0], d4["v"][0], d4["w"], d4["u"], d4["s0"][0], 12, ns[:17])
     s_t, y_t = torch_ref.wkv4_base_torch(*[torch.tensor(x) for x in (d4["r"][0], d4["k"][0], d4["v"][0], d4["w"], d4["u"], d4["s0"][0])], 12, torch.tensor(ns[:17]))
     assert rel_err(y_t.numpy(), y_np) < 1e-12 and rel_err(s_t.numpy(), s_np) < 1e-12
+
+
+def test_token_shift_matches_reference_fixture(golden):
+    """Fixture made by the reference's own channel_mixing_seq with identity matrices (make_golden.run_shift)."""
+    from oracle import token_shift as ts
+    g = golden("v7_token_shift")
+    for i in range(g["in_x"].shape[0]):
+        mixed, last = ts.token_shift(g["in_x"][i].astype(np.float64), g["in_prev"][i].astype(np.float64),
+                                     g["in_mix"].astype(np.float64), int(g["in_length"][i]), g["in_new_starts"][i])
+        assert rel_err(mixed[0], g["xk"][i]) < 1e-12
+        np.testing.assert_array_equal(last, g["last"][i])
