@@ -407,6 +407,39 @@ wkv7_seq_bwd_kernel(int Tlen, int H, const T* __restrict__ w, const T* __restric
         store4(ds0 + tile_base + ii * kN, make_float4(dS[ii][0], dS[ii][1], dS[ii][2], dS[ii][3]));
 }
 
+// sixteen consecutive state elements of one thread, moved with 16-byte accesses
+__device__ __forceinline__ void load16(const float* p, float* f) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) *reinterpret_cast<float4*>(f + g * 4) = __ldg(reinterpret_cast<const float4*>(p) + g);
+}
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float* f) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p) + g);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 t = __bfloat1622float2(h[e]);
+            f[g * 8 + 2 * e] = t.x;
+            f[g * 8 + 2 * e + 1] = t.y;
+        }
+    }
+}
+__device__ __forceinline__ void store16(float* p, const float* f) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) reinterpret_cast<float4*>(p)[g] = *reinterpret_cast<const float4*>(f + g * 4);
+}
+__device__ __forceinline__ void store16(__nv_bfloat16* p, const float* f) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[g * 8 + 2 * e], f[g * 8 + 2 * e + 1]);
+        reinterpret_cast<uint4*>(p)[g] = raw;
+    }
+}
+
 // ------------------------------------------------------------------ single step -----
 // T == 1 (recurrent decoding): the whole cost is reading and writing the 64x64 state once, so the
 // kernel is a straight HBM stream.  256 threads per (batch, head): thread (i = tid/4, q = tid%4) owns
@@ -430,16 +463,9 @@ wkv7_step_kernel(int H, const T* __restrict__ w, const T* __restrict__ r, const 
     }
     const size_t st = ((size_t)bh * kN + i) * kN + q * 16;
     float S[16];
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-        const float4 x = load4(s0 + st + g * 4);
-        S[g * 4] = x.x; S[g * 4 + 1] = x.y; S[g * 4 + 2] = x.z; S[g * 4 + 3] = x.w;
-    }
+    load16(s0 + st, S);
     const bool keep_input = (length[bi] == 0);   // length == 0 returns the input state untouched
-    if (keep_input) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) store4(s_out + st + g * 4, make_float4(S[g * 4], S[g * 4 + 1], S[g * 4 + 2], S[g * 4 + 3]));
-    }
+    if (keep_input) store16(s_out + st, S);
     if (new_starts[bi]) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) S[j] = 0.f;
@@ -461,10 +487,7 @@ wkv7_step_kernel(int H, const T* __restrict__ w, const T* __restrict__ r, const 
     yy += __shfl_xor_sync(0xffffffffu, yy, 1);
     yy += __shfl_xor_sync(0xffffffffu, yy, 2);
     if (q == 0) y[(size_t)bh * kN + i] = from_f32<T>(yy);
-    if (!keep_input) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) store4(s_out + st + g * 4, make_float4(S[g * 4], S[g * 4 + 1], S[g * 4 + 2], S[g * 4 + 3]));
-    }
+    if (!keep_input) store16(s_out + st, S);
 }
 
 // ------------------------------------------------------------------ launchers -------
@@ -500,9 +523,16 @@ static int launch_bwd(cudaStream_t st, int B, int Tlen, int H, const void* w, co
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
+int wkv7_step_stream(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
+                     const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+                     void* s_out);
+
 int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
               const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
               void* s_out) {
+    // states on 16-byte boundaries (every framework allocation is) take the pipelined stream kernel
+    if (((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s_out)) & 15u) == 0)
+        return wkv7_step_stream(st, dtype, B, H, w, r, k, v, a, b, s0, length, ns, y, s_out);
     if (dtype == B200WKV_F32)
         wkv7_step_kernel<float><<<B * H, 256, 0, st>>>(H, (const float*)w, (const float*)r, (const float*)k, (const float*)v,
                                                        (const float*)a, (const float*)b, (const float*)s0, length, ns,

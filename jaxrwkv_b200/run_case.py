@@ -26,6 +26,25 @@ def decode(a):
     nbytes = a.batch * a.heads * (2 * 64 * 64 + 7 * 64) * st.element_size()
     print(f"decode B={a.batch} H={a.heads} {dtype}: {us:.1f} us/step, {a.batch / us:.2f} M tokens/s per layer, "
           f"{nbytes / us / 1e3:.0f} GB/s of state+vector traffic")
+    # the same chain replayed from a CUDA graph: launch overhead of the host loop taken out
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        g_st = st.clone()
+        with torch.cuda.graph(graph, stream=side):
+            cur = g_st
+            for _ in range(a.iters):
+                cur, y = rwkv7.wkv7_step(*args, cur)
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = 1e3 * e0.elapsed_time(e1) / a.iters
+    print(f"decode B={a.batch} H={a.heads} {dtype} (CUDA graph of {a.iters} steps): {us:.1f} us/step, "
+          f"{a.batch / us:.2f} M tokens/s per layer, {nbytes / us / 1e3:.0f} GB/s of state+vector traffic")
 
 
 def main():

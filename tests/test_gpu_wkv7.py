@@ -378,6 +378,43 @@ def test_decode_step_kernel(dtype):
     assert rel_err(npf(torch.stack(outs, 1)), yo) < 1e-4 and rel_err(npf(st), so) < 1e-4
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_step_many_pairs_ring_wraps(dtype):
+    """More (batch, head) pairs than resident CTAs times ring stages, so every CTA refills each
+    stage of its ring several times; compared with the T-loop kernels on the same one-token inputs."""
+    B, H = 192, 40
+    g = torch.Generator(device="cuda").manual_seed(5)
+    shp = (B, 1, H, 64)
+    r, k, v = (torch.randn(shp, device="cuda", generator=g).to(dtype) for _ in range(3))
+    w = (-0.5 - torch.nn.functional.softplus(torch.randn(shp, device="cuda", generator=g))).to(dtype)
+    kk = torch.nn.functional.normalize(torch.randn(shp, device="cuda", generator=g), dim=-1)
+    a, b = (-kk).to(dtype), (kk * torch.rand(shp, device="cuda", generator=g)).to(dtype)
+    s0 = (0.5 * torch.randn(B, H, 64, 64, device="cuda", generator=g)).to(dtype)
+    length = torch.ones(B, dtype=torch.int32, device="cuda")
+    length[7] = 0
+    ns = torch.zeros(B, 1, dtype=torch.uint8, device="cuda")
+    ns[3] = 1
+    ns[190] = 1
+    (s1, y1), _ = rwkv7.batched_wkv7_fwd(r, w, k, v, a, b, s0, length, ns, B, need_residual=False)
+    # the recurrence of one token in float64 (rwkv7.py:199-220), state indexed [value][key]
+    f = lambda x: x.double().squeeze(1)
+    S = torch.where(ns.bool()[:, :, None, None], torch.zeros_like(s0, dtype=torch.float64), s0.double())
+    sa = torch.einsum("bhij,bhj->bhi", S, f(a))
+    S = S * torch.exp(-torch.exp(f(w)))[:, :, None, :] + f(v)[..., :, None] * f(k)[..., None, :] + sa[..., :, None] * f(b)[..., None, :]
+    y2 = torch.einsum("bhij,bhj->bhi", S, f(r)).unsqueeze(1)
+    s2 = torch.where((length > 0)[:, None, None, None], S, s0.double())
+    rows = [(i, rel_err(npf(y1[i]), y2[i].cpu().numpy())) for i in range(B)]
+    assert max(e for _, e in rows) < TOL[dtype], sorted(rows, key=lambda t: -t[1])[:5]
+    assert rel_err(npf(s1), s2.cpu().numpy()) < TOL[dtype]
+    assert torch.equal(s1[7], s0[7])
+    # the T-loop kernels on the same one-token problem
+    (s3, y3), _ = rwkv7.batched_wkv7_fwd(r, w, k, v, a, b, s0, length, ns, B, need_residual=True,
+                                         flags=_lib.FLAG_SEQUENTIAL)
+    rows = [(i, rel_err(npf(y3[i]), y2[i].cpu().numpy())) for i in range(B)]
+    assert max(e for _, e in rows) < TOL[dtype], sorted(rows, key=lambda t: -t[1])[:5]
+    assert rel_err(npf(s3), s2.cpu().numpy()) < TOL[dtype]
+
+
 def test_no_bounded_wait_ran_out_during_the_suite():
     """Every mbarrier wait in the tensor-core kernels is bounded and records a failure in a device
     word; after the tensor-core tests above that word must still be clear."""
