@@ -17,8 +17,71 @@ constexpr float kLn2 = 0.6931471805599453f;
 // Residual written by the chunked forward for the chunked backward (all fp32):
 //   [B*H][ceil(T/64)][64][64]  state entering every 64-token block (before a start flag is applied)
 //   [B*H][64][64]              state at position `length` (what the forward returns as s_out)
-inline size_t chunk_residual_floats(int B, int T, int H) {
+//   [kHandoffSlots][64*64 + 64] carries passed between CTAs that share one (batch, head) sequence
+//   [kHandoffSlots]             their ready flags (int)
+// The last two are scratch of whichever kernel runs: a sequence may be cut at 64-token block
+// boundaries into runs owned by neighbouring CTAs, so that B*H sequences spread evenly over the SMs.
+constexpr int kHandoffSlots = 512;
+constexpr int kHandoffFloats = kN * kN + kN;
+inline size_t chunk_states_floats(int B, int T, int H) {
     return (size_t)B * H * ((size_t)((T + kC - 1) / kC) + 1) * kN * kN;
+}
+inline size_t chunk_residual_floats(int B, int T, int H) {
+    return chunk_states_floats(B, T, H) + (size_t)kHandoffSlots * (kHandoffFloats + 1);
+}
+
+// Host side of the split: grid size and segments per sequence for `chains` sequences of `n_blk`
+// blocks with `per_sm` resident CTAs per SM.
+struct SplitPlan {
+    int grid;
+    int seg;
+};
+inline SplitPlan plan_split(int chains, int n_blk, int per_sm) {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    const int slots = sm_count * per_sm;
+    SplitPlan p{chains, 1};
+    if (chains <= slots) return p;            // every sequence gets its own resident CTA
+    p.grid = slots;
+    if (chains % slots == 0 || slots > kHandoffSlots) return p;
+    // makespan in sequence lengths is ceil(chains * seg / slots) / seg: take the smallest seg that helps
+    double best = (double)((chains + slots - 1) / slots);
+    for (int seg = 2; seg <= 8 && seg <= n_blk; seg *= 2) {
+        const double m = (double)(((long long)chains * seg + slots - 1) / slots) / seg;
+        if (m < best * 0.98) {
+            best = m;
+            p.seg = seg;
+        }
+    }
+    return p;
+}
+
+// Work split of U = (sequences x segments) units over G CTAs: CTA c owns units [U c / G, U (c+1) / G).
+// Units are numbered sequence-major; the consecutive units of one sequence inside a CTA's range form
+// a run that the CTA walks as one piece.  A CTA whose range ends inside a sequence walks that run
+// FIRST and hands its carry to the next CTA (slot c); the run at the start of its range that begins
+// inside a sequence comes LAST and takes the carry of slot c - 1.  No CTA waits before it has
+// produced what its neighbour needs, so the waits cannot form a cycle.
+struct RunPlan {
+    int chain;      // sequence index (batch * H + head)
+    int seg_from;   // first segment of the run, in walking order
+    int seg_to;     // one past the last segment
+};
+__device__ __forceinline__ int run_count(long long lo, long long hi, int seg) { return (int)((hi - 1) / seg - lo / seg) + 1; }
+__device__ __forceinline__ RunPlan run_at(long long lo, long long hi, int seg, int order) {
+    const int first = (int)(lo / seg), n = run_count(lo, hi, seg);
+    // walking order: the last run of the range, the middle runs, the first run of the range
+    const int ri = (n == 1) ? 0 : (order == 0 ? n - 1 : (order == n - 1 ? 0 : order));
+    RunPlan r;
+    r.chain = first + ri;
+    r.seg_from = (ri == 0) ? (int)(lo % seg) : 0;
+    r.seg_to = (ri == n - 1) ? (int)((hi - 1) % seg) + 1 : seg;
+    return r;
 }
 
 __device__ __forceinline__ uint32_t pack2(float x, float y) {

@@ -95,18 +95,22 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const float* __restrict__ ckpt, const float* __restrict__ s_at_len,
                       __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ dr, __nv_bfloat16* __restrict__ dk,
                       __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
-                      __nv_bfloat16* __restrict__ ds0, int* __restrict__ status) {
+                      __nv_bfloat16* __restrict__ ds0, int* __restrict__ status, int BH, int SEG,
+                      float* __restrict__ carry, int* __restrict__ carry_flag) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
-    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = warp & 3, hsel = warp >> 2;     // TMEM lane quadrant / column half handled by this warp
     const int row = quad * 32 + lane;                // TMEM lane == tile row
-    const int L = min((int)length[bi], Tlen);
     const size_t tok_stride = (size_t)H * kN;
-    const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
-    const size_t st_base = (size_t)bh * kN * kN;
     const int nBlk = (Tlen + kC - 1) / kC;
+    // the sequence this CTA currently walks (set per run)
+    int bh = 0, bi = 0, L = 0;
+    size_t seq_base = 0, st_base = 0;
+    // units [unit_lo, unit_hi) of the (sequence, segment) list belong to this CTA
+    const long long unit_lo = (long long)BH * SEG * blockIdx.x / gridDim.x;
+    const long long unit_hi = (long long)BH * SEG * (blockIdx.x + 1) / gridDim.x;
+    const int n_runs = run_count(unit_lo, unit_hi, SEG);
 
     if (tid == 0) {
 #pragma unroll
@@ -117,8 +121,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     float* dsf = reinterpret_cast<float*>(smem + OFF_DSF);   // [64][LF_PITCH]
     float* cum = reinterpret_cast<float*>(smem + OFF_CUM);   // [64][LF_PITCH]
     float* lf = reinterpret_cast<float*>(smem + OFF_LF);     // [64][LF_PITCH]
-    for (int idx = tid; idx < 64 * LF_PITCH; idx += 256) dsf[idx] = 0.f;
-    if (tid < 64) sm.d_in[tid] = 0.f;
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -205,7 +207,46 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
     };
-    plan_block(blk);
+    for (int order = 0; order < n_runs; ++order) {
+    const RunPlan run = run_at(unit_lo, unit_hi, SEG, order);
+    bh = run.chain;
+    bi = bh / H;
+    L = min((int)length[bi], Tlen);
+    seq_base = (size_t)bi * Tlen * tok_stride + (size_t)(bh % H) * kN;
+    st_base = (size_t)bh * kN * kN;
+    // segments are counted from the end of the sequence: segment j covers blocks
+    // [nBlk (SEG-1-j) / SEG, nBlk (SEG-j) / SEG)
+    const int blk_hi = (int)((long long)nBlk * (SEG - run.seg_from) / SEG);
+    const int blk_lo = (int)((long long)nBlk * (SEG - run.seg_to) / SEG);
+    const int tok_lo = blk_lo * kC;
+    __syncthreads();   // the previous run has finished with dsf and d_in
+    if (run.seg_from == 0) {
+        for (int idx = tid; idx < 64 * LF_PITCH; idx += 256) dsf[idx] = 0.f;
+        if (tid < 64) sm.d_in[tid] = 0.f;
+    } else {
+        // the later part of this sequence was walked by the previous CTA: take over its carry
+        const int slot = (int)blockIdx.x - 1;
+        if (tid == 0) {
+            bool ready = false;
+            for (uint32_t it = 0; it < (1u << 24) && !ready; ++it) {
+                int f;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(carry_flag + slot) : "memory");
+                ready = f != 0;
+                if (!ready) __nanosleep(64);
+            }
+            sm.nsm[0] = ready ? 1u : 0u;
+        }
+        __syncthreads();
+        if (sm.nsm[0] == 0u) failed = true;
+        const float* src = carry + (size_t)slot * kHandoffFloats;
+        for (int idx = tid; idx < 64 * 16; idx += 256) {
+            const int rr = idx >> 4, c4 = (idx & 15) * 4;
+            *reinterpret_cast<float4*>(&dsf[rr * LF_PITCH + c4]) = __ldcg(reinterpret_cast<const float4*>(src + rr * kN + c4));
+        }
+        if (tid < 64) sm.d_in[tid] = __ldcg(src + kN * kN + tid);
+    }
+    blk = blk_hi - 1;
+    plan_block(blk);   // begins and ends with a barrier: dsf and d_in are in place afterwards
     p1 = be;
     plan_chunk(p1);
     while (true) {
@@ -563,7 +604,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 // ---------------- plan the next chunk and issue its loads; the rest of this chunk is the scan
                 cur_p = p; cur_n = n; cur_reset = reset_here;
-                has_next = cur_p > 0;
+                has_next = cur_p > tok_lo;
                 if (has_next) {
                     if (cur_p == bs) plan_block(--blk);
                     plan_chunk(cur_p);
@@ -640,7 +681,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
     }
     __syncthreads();
-    {   // gradient with respect to the initial state
+    if (run.seg_to == SEG) {   // the sequence is complete: gradient with respect to the initial state
         float g[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) g[e] = dsf[si * LF_PITCH + scq * 16 + e];
@@ -653,7 +694,21 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         *reinterpret_cast<uint4*>(ds0 + st_base + si * kN + scq * 16) = pack8(g);
         *reinterpret_cast<uint4*>(ds0 + st_base + si * kN + scq * 16 + 8) = pack8(g + 8);
+    } else {                   // the next CTA walks the earlier part: hand the carry over
+        float* dst = carry + (size_t)blockIdx.x * kHandoffFloats;
+        for (int idx = tid; idx < 64 * 16; idx += 256) {
+            const int rr = idx >> 4, c4 = (idx & 15) * 4;
+            __stcg(reinterpret_cast<float4*>(dst + rr * kN + c4), *reinterpret_cast<const float4*>(&dsf[rr * LF_PITCH + c4]));
+        }
+        if (tid < 64) __stcg(dst + kN * kN + tid, sm.d_in[tid]);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int one = 1;
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(carry_flag + blockIdx.x), "r"(one) : "memory");
+        }
     }
+    }   // runs
     if (failed && status != nullptr) atomicExch(status, 2);
     tc::fence_before_sync();
     __syncthreads();
@@ -681,11 +736,35 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     if (cudaFuncSetAttribute(wkv7_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
         return B200WKV_ELAUNCH;
     const float* ck = (const float*)residual;
-    const float* sl = ck + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN;
-    wkv7_chunk_bwd_kernel<<<B * H, 256, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
-                                                          (const bf*)a, (const bf*)b, length, ns, (const bf*)dy,
-                                                          (const bf*)ds_out, ck, sl, (bf*)dw, (bf*)dr, (bf*)dk,
-                                                          (bf*)dv, (bf*)da, (bf*)db, (bf*)ds0, wkv7_chunk_status_word());
+    const int nBlk = (T + kC - 1) / kC;
+    const float* sl = ck + (size_t)B * H * nBlk * kN * kN;
+    // the tail of the buffer is scratch for carries between CTAs (see chunk_residual_floats)
+    float* carry = const_cast<float*>(ck) + chunk_states_floats(B, T, H);
+    int* carry_flag = reinterpret_cast<int*>(carry + (size_t)kHandoffSlots * kHandoffFloats);
+    const bf *pw = (const bf*)w, *pr = (const bf*)r, *pk = (const bf*)k, *pv = (const bf*)v, *pa = (const bf*)a, *pb = (const bf*)b;
+    const bf *pdy = (const bf*)dy, *pds = (const bf*)ds_out;
+    bf *gw = (bf*)dw, *gr = (bf*)dr, *gk = (bf*)dk, *gv = (bf*)dv, *ga = (bf*)da, *gb = (bf*)db, *gs = (bf*)ds0;
+    int* status = wkv7_chunk_status_word();
+    int BH = B * H;
+    // One CTA per SM (shared memory).  With more sequences than SMs the CTAs are persistent; when
+    // the sequences do not divide evenly, each is cut into `seg` runs of blocks so that every CTA
+    // gets the same number of units, and neighbouring CTAs pass the carry through global memory.
+    const SplitPlan plan = plan_split(BH, nBlk, 1);
+    if (plan.seg > 1) {
+        if (cudaMemsetAsync(carry_flag, 0, (size_t)kHandoffSlots * sizeof(int), st) != cudaSuccess) return B200WKV_ELAUNCH;
+        int Tl = T, Hl = H, seg = plan.seg;
+        void* args[] = {&Tl, &Hl, &pw, &pr, &pk, &pv, &pa, &pb, &length, &ns, &pdy, &pds, &ck, &sl, &gw, &gr, &gk, &gv, &ga,
+                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag};
+        // cooperative launch: the runtime guarantees that all CTAs are resident at once, which the
+        // carry hand-over relies on; if it refuses, fall through to one CTA per sequence
+        if (cudaLaunchCooperativeKernel((const void*)wkv7_chunk_bwd_kernel, dim3(plan.grid), dim3(256), args, SMEM_BYTES, st) ==
+            cudaSuccess)
+            return B200WKV_OK;
+        (void)cudaGetLastError();
+    }
+    wkv7_chunk_bwd_kernel<<<plan.seg > 1 ? BH : plan.grid, 256, SMEM_BYTES, st>>>(T, H, pw, pr, pk, pv, pa, pb, length, ns, pdy, pds, ck,
+                                                                               sl, gw, gr, gk, gv, ga, gb, gs, status, BH, 1,
+                                                                               carry, carry_flag);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

@@ -325,13 +325,34 @@ def test_chunk_bwd_full_size_properties():
         assert torch.equal(a, b)
         assert torch.equal(c, a * 2)
     # spot-check two (batch, head) slices against the oracle
-    for bi, hh in ((0, 0), (7, 31)):
+    for bi, hh in ((0, 0), (0, 1), (0, 3), (7, 31)):   # (0, 1) and (0, 3) are walked by two CTAs each on 148 SMs
         ins = [t[n][bi:bi + 1, :, hh:hh + 1].double().cpu().numpy() for n in NAMES7[:-1]] + [t["s0"][bi:bi + 1, hh:hh + 1].double().cpu().numpy()]
         ref = oracle.wkv7_bwd_batched(*ins, d["length"][bi:bi + 1], d["new_starts"][bi:bi + 1],
                                       npf(gy[bi:bi + 1, :, hh:hh + 1]), npf(gs[bi:bi + 1, hh:hh + 1]))
         got = [g1[i][bi:bi + 1, :, hh:hh + 1] for i in range(6)] + [g1[6][bi:bi + 1, hh:hh + 1]]
         for n, a, b in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), got, ref):
             assert rel_err(npf(a), b) < TOL[torch.bfloat16], (n, bi, hh, rel_err(npf(a), b))
+
+
+@pytest.mark.parametrize("T", [300, 512])
+def test_chunk_bwd_sequences_split_across_ctas(T):
+    """More sequences than SMs and not a multiple of them: the tensor-core backward cuts sequences
+    into runs of blocks owned by neighbouring CTAs.  Ragged lengths and start flags; every gradient
+    against the token-sequential kernels on the same inputs."""
+    B, H = 5, 37
+    d = wkv7_case(B, T, H, seed=4321 + T, s0_scale=0.3, p_start=1 / 100, random_length=True)
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    s, y, res = run_fwd(t, length, ns)
+    gy = torch.randn_like(y); gs = torch.randn_like(s)
+    g1 = rwkv7.batched_wkv7_bwd(res, (gs, gy), B)
+    g1b = rwkv7.batched_wkv7_bwd(res, (gs, gy), B)
+    s_q, y_q, res_q = run_fwd(t, length, ns, _lib.FLAG_SEQUENTIAL)
+    g2 = rwkv7.batched_wkv7_bwd(res_q, (gs, gy), B, flags=_lib.FLAG_SEQUENTIAL)
+    for n, a, a2, b in zip(("dr", "dw", "dk", "dv", "da", "db", "ds0"), g1, g1b, g2):
+        assert torch.equal(a, a2), n
+        for bi in range(B):
+            assert rel_err(npf(a[bi]), npf(b[bi])) < TOL[torch.bfloat16], (n, bi, rel_err(npf(a[bi]), npf(b[bi])))
 
 
 def test_host_pipeline_matches_device_path():
