@@ -96,6 +96,15 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// Tiled copy of one box of a 2-D tensor map into this CTA's shared memory.  x (innermost coordinate)
+// times the element size must be a multiple of 16 bytes; the destination 128-byte aligned.
+__device__ __forceinline__ void tensor_load_2d(void* dst_smem, const void* tmap, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 // shared -> global; completion is tracked per thread in bulk groups
 __device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(__cvta_generic_to_global(dst_gmem)),

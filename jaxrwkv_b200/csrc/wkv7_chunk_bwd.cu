@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "tc05.cuh"
 #include "chunk_common.cuh"
+#include "tmap.cuh"
 
 namespace b200wkv {
 
@@ -47,7 +48,16 @@ constexpr int OFF_CUM = OFF_LF + LF_PITCH * 64 * 4;   // fp32 cumulative log-dec
 constexpr int OFF_DSF = OFF_CUM + LF_PITCH * 64 * 4;   // fp32 dS carried across chunks [64][LF_PITCH]
 constexpr int OFF_XINV = OFF_DSF + LF_PITCH * 64 * 4; // fp32 (I - A_ab)^-1
 constexpr int OFF_SCR = OFF_XINV + LF_PITCH * 64 * 4;    // scratch of the inverse
-constexpr int OFF_SMALL = OFF_SCR + TRI_SCR_FLOATS * 4;
+// Staging tiles for the raw rows of the NEXT chunk (7 streams x 64 tokens x 128 bytes), filled by bulk
+// asynchronous copies while the current chunk finishes.  Tiles 0..4 lie over XINV, SCR and a tail kept
+// for them (all idle once the inverse has been converted), tiles 5..6 over TINV + A_ak (idle once the
+// fourth round of products has completed).
+constexpr int STG_TILE = kC * kN * 2;
+constexpr int OFF_STG = OFF_XINV;
+constexpr int STG_TAIL = 5 * STG_TILE - (LF_PITCH * 64 * 4 + TRI_SCR_FLOATS * 4);
+constexpr int OFF_SMALL = OFF_SCR + TRI_SCR_FLOATS * 4 + STG_TAIL;
+static_assert(STG_TAIL >= 0 && 2 * STG_TILE <= 2 * SLAB64, "staging tiles must fit their hosts");
+__device__ __forceinline__ int stage_off(int m) { return m < 5 ? OFF_STG + m * STG_TILE : OFF_TINV + (m - 5) * STG_TILE; }
 static_assert(2 * SLAB128 <= 4 * SLAB64, "W must fit over the X region");
 struct Small {
     float h1[kN];
@@ -56,7 +66,7 @@ struct Small {
     float d_in[kN];        // D carried from the chunk processed before (later in time)
     float d_part[2][kN];   // partial column sums of the new anchor
     float seg[4][kN];      // per-16-token totals of the decay-gradient scan
-    uint64_t bar[5];
+    uint64_t bar[6];       // 0..4 product rounds, 5 staging tiles
     uint32_t nsm[2];       // chunk starts inside the current 64-token block
     uint32_t nsf[2];       // start flags inside the current block
     uint32_t tmem;
@@ -80,6 +90,11 @@ __device__ long long g_prof_bwd[24];   // cycles per phase, summed over the chun
 #define PROF_MARK(i) do { } while (0)
 #endif
 
+// tensor maps of the seven streams w, r, k, v, a, b, dy viewed as [B*T tokens][H*64 channels]
+struct StreamMaps {
+    CUtensorMap m[7];
+};
+
 // four K=16 steps (64 deep) of D (+)= A B
 __device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, bool accumulate) {
 #pragma unroll
@@ -96,7 +111,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ dr, __nv_bfloat16* __restrict__ dk,
                       __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
                       __nv_bfloat16* __restrict__ ds0, int* __restrict__ status, int BH, int SEG,
-                      float* __restrict__ carry, int* __restrict__ carry_flag) {
+                      float* __restrict__ carry, int* __restrict__ carry_flag, const __grid_constant__ StreamMaps maps) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -114,7 +129,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 5; ++i) tc::mbar_init(&sm.bar[i], 1);
+        for (int i = 0; i < 6; ++i) tc::mbar_init(&sm.bar[i], 1);
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(&sm.tmem, 512);
@@ -142,7 +157,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     const int tsub = tid >> 3, jb = tid & 7;   // staging unit: tokens 32q + tsub (q = 0,1), channels 8jb..8jb+7
     const int si = tid & 63, scq = tid >> 6;   // state element ownership: row si, columns 16scq..16scq+15
-    uint32_t par = 0;
+    uint32_t par = 0, spar = 0;   // phase parities of the product barriers and of the staging barrier
 #ifdef WKV_PROF
     long long prof_t_ = clock64();
 #endif
@@ -180,30 +195,34 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         n = end - p;
         reset_here = ((fmask >> (p - bs)) & 1ull) != 0;
     };
-    auto issue_loads = [&]() {
+    // the 64 token rows from cp on of the seven streams into the staging tiles: one tiled copy of
+    // 64 x 128 bytes per stream, all issued by thread 0.  Rows past the chunk arrive too and are ignored.
+    const int n_streams = (dy != nullptr) ? 7 : 6;
+    auto issue_stage = [&](int cp) {
+        if (tid == 0) {
+            tc::mbar_expect_tx(&sm.bar[5], (uint32_t)(n_streams * STG_TILE));
+            const int x = (bh % H) * kN, y = bi * Tlen + cp;
+#pragma unroll
+            for (int m = 0; m < 7; ++m)
+                if (m < n_streams) tc::tensor_load_2d(smem + stage_off(m), &maps.m[m], x, y, &sm.bar[5]);
+        }
+    };
+    auto take_stage = [&]() {
+        if (!tc::mbar_wait(&sm.bar[5], spar)) failed = true;
+        spar ^= 1u;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const int t = q * 32 + tsub;
             if (t < n) {
-                const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
-                wraw[q] = __ldg(reinterpret_cast<const uint4*>(w + g));
-                raw[q][0] = __ldg(reinterpret_cast<const uint4*>(r + g));
-                raw[q][1] = __ldg(reinterpret_cast<const uint4*>(k + g));
-                raw[q][2] = __ldg(reinterpret_cast<const uint4*>(v + g));
-                raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
-                raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
-                raw[q][5] = (dy != nullptr) ? __ldg(reinterpret_cast<const uint4*>(dy + g)) : make_uint4(0, 0, 0, 0);
+                const int o = t * (kN * 2) + jb * 16;
+                wraw[q] = *reinterpret_cast<const uint4*>(smem + stage_off(0) + o);
+#pragma unroll
+                for (int m = 0; m < 5; ++m) raw[q][m] = *reinterpret_cast<const uint4*>(smem + stage_off(m + 1) + o);
+                raw[q][5] = (dy != nullptr) ? *reinterpret_cast<const uint4*>(smem + stage_off(6) + o) : make_uint4(0, 0, 0, 0);
             } else {
                 wraw[q] = make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (int m = 0; m < 6; ++m) raw[q][m] = make_uint4(0, 0, 0, 0);
-            }
-            // pull the lines of the 64 tokens in front of this chunk (processed after it) towards L2
-            if (jb == 0 && p - kC + t >= 0) {
-                const size_t gn = seq_base + (size_t)(p - kC + t) * tok_stride;
-                prefetch_l2(w + gn); prefetch_l2(r + gn); prefetch_l2(k + gn); prefetch_l2(v + gn);
-                prefetch_l2(a + gn); prefetch_l2(b + gn);
-                if (dy != nullptr) prefetch_l2(dy + gn);
             }
         }
     };
@@ -249,9 +268,12 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     plan_block(blk);   // begins and ends with a barrier: dsf and d_in are in place afterwards
     p1 = be;
     plan_chunk(p1);
+    tc::fence_async_smem();   // the tiles' hosts were last written by ordinary stores
+    __syncthreads();
+    issue_stage(p);
     while (true) {
         {
-            issue_loads();
+            take_stage();
             // ---------------- cotangent of the returned state enters at position `length` ----------------
             if (p1 == L && ds_out != nullptr) {
                 float g[16];
@@ -454,6 +476,14 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             PROF_MARK(11);
             if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
             tc::fence_after_sync();
+            // ---------------- plan the next chunk (earlier in time) ----------------
+            const int cur_p = p, cur_n = n;
+            const bool cur_reset = reset_here;
+            const bool has_next = cur_p > tok_lo;
+            if (has_next) {
+                if (cur_p == bs) plan_block(--blk);
+                plan_chunk(cur_p);
+            }
             {
                 const int t = row & 63;
                 float d[64];
@@ -472,8 +502,8 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 float x[32];
                 tc::tmem_ld32(lane_addr + T_GD + hsel * 32, x);
                 tc::tmem_wait_ld();
-                if (t < n) {
-                    __nv_bfloat16* dst = dv + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+                if (t < cur_n) {
+                    __nv_bfloat16* dst = dv + seq_base + (size_t)(cur_p + t) * tok_stride + hsel * 32;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&x[c * 8]);
                 }
@@ -527,13 +557,14 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_G, mnmaj128(sWY), mnmaj128(sBK + HALF), ID_MM, true);
                 tc::commit(&sm.bar[4]);
             }
+            // the rows of the next chunk (earlier in time) start travelling while the products run: their
+            // tiles lie over buffers that the fourth round was the last to read
+            if (has_next) issue_stage(p);
             PROF_MARK(13);
             // everything of the epilogue that does not depend on the products runs while they execute:
             // decay factors of this row and the operand rows it pairs with (kept packed)
             float fx[32], fz[32], lwt[32];
             uint4 s1raw[4], s2raw[4];
-            int cur_p, cur_n;
-            bool cur_reset, has_next;
             {
                 const int t = row & 63;
                 const unsigned char* slab1 = smem + OFF_AR + ((row < 64) ? (64 + t) * 16 : t * 16);   // R~ / A~
@@ -592,8 +623,8 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         z[e] *= fz[e];
                     }
                 }
-                if (t < n) {
-                    const size_t g = seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+                if (t < cur_n) {
+                    const size_t g = seq_base + (size_t)(cur_p + t) * tok_stride + hsel * 32;
                     __nv_bfloat16* dx = (row < 64) ? dk : db;
                     __nv_bfloat16* dz = (row < 64) ? dr : da;
 #pragma unroll
@@ -601,13 +632,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         *reinterpret_cast<uint4*>(dx + g + c * 8) = pack8(&x[c * 8]);
                         *reinterpret_cast<uint4*>(dz + g + c * 8) = pack8(&z[c * 8]);
                     }
-                }
-                // ---------------- plan the next chunk and issue its loads; the rest of this chunk is the scan
-                cur_p = p; cur_n = n; cur_reset = reset_here;
-                has_next = cur_p > tok_lo;
-                if (has_next) {
-                    if (cur_p == bs) plan_block(--blk);
-                    plan_chunk(cur_p);
                 }
             PROF_MARK(15);
                 // u_t = (r dr - k dk) + (a da - b db): first the dk/dr rows write, then the db/da rows add
@@ -746,6 +770,10 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     bf *gw = (bf*)dw, *gr = (bf*)dr, *gk = (bf*)dk, *gv = (bf*)dv, *ga = (bf*)da, *gb = (bf*)db, *gs = (bf*)ds0;
     int* status = wkv7_chunk_status_word();
     int BH = B * H;
+    StreamMaps maps;
+    const void* bases[7] = {w, r, k, v, a, b, dy != nullptr ? dy : w};
+    for (int m = 0; m < 7; ++m)
+        if (!make_tmap_bf16_2d(&maps.m[m], bases[m], (uint64_t)B * T, (uint64_t)H * kN, kC, kN)) return B200WKV_ELAUNCH;
     // One CTA per SM (shared memory).  With more sequences than SMs the CTAs are persistent; when
     // the sequences do not divide evenly, each is cut into `seg` runs of blocks so that every CTA
     // gets the same number of units, and neighbouring CTAs pass the carry through global memory.
@@ -754,7 +782,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
         if (cudaMemsetAsync(carry_flag, 0, (size_t)kHandoffSlots * sizeof(int), st) != cudaSuccess) return B200WKV_ELAUNCH;
         int Tl = T, Hl = H, seg = plan.seg;
         void* args[] = {&Tl, &Hl, &pw, &pr, &pk, &pv, &pa, &pb, &length, &ns, &pdy, &pds, &ck, &sl, &gw, &gr, &gk, &gv, &ga,
-                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag};
+                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps};
         // cooperative launch: the runtime guarantees that all CTAs are resident at once, which the
         // carry hand-over relies on; if it refuses, fall through to one CTA per sequence
         if (cudaLaunchCooperativeKernel((const void*)wkv7_chunk_bwd_kernel, dim3(plan.grid), dim3(256), args, SMEM_BYTES, st) ==
@@ -764,7 +792,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     }
     wkv7_chunk_bwd_kernel<<<plan.seg > 1 ? BH : plan.grid, 256, SMEM_BYTES, st>>>(T, H, pw, pr, pk, pv, pa, pb, length, ns, pdy, pds, ck,
                                                                                sl, gw, gr, gk, gv, ga, gb, gs, status, BH, 1,
-                                                                               carry, carry_flag);
+                                                                               carry, carry_flag, maps);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
