@@ -40,4 +40,15 @@ inline bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor maps of up to seven bf16 streams viewed as [B*T tokens][H*64 channels]; a box is the 64 rows
+// x 64 channels of one head from one token on (8 KB, rows of 128 bytes in shared memory).
+struct StreamMaps {
+    CUtensorMap m[7];
+};
+inline bool make_stream_maps(StreamMaps* out, const void* const* bases, int count, int B, int T, int H) {
+    for (int m = 0; m < 7; ++m)
+        if (!make_tmap_bf16_2d(&out->m[m], bases[m < count ? m : 0], (uint64_t)B * T, (uint64_t)H * 64, 64, 64)) return false;
+    return true;
+}
+
 }  // namespace b200wkv

@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "tc05.cuh"
 #include "chunk_common.cuh"
+#include "tmap.cuh"
 
 namespace b200wkv {
 
@@ -42,11 +43,16 @@ constexpr int OFF_LF = OFF_AR;                           // fp32 A_ab
 constexpr int OFF_X = OFF_LF + LF_PITCH * 64 * 4;        // fp32 (I - A_ab)^-1
 constexpr int OFF_SCR = OFF_X + LF_PITCH * 64 * 4;       // scratch of the inverse
 constexpr int OFF_CUM = OFF_TP;
+// Staging tiles for the raw rows of the NEXT chunk (6 streams x 64 tokens x 128 bytes), filled by tiled
+// bulk copies once the inverse is done: tiles 0..4 over AR + BK + S0, tile 5 over the P_rk half of M2A.
+constexpr int STG_TILE = kC * kN * 2;
+static_assert(5 * STG_TILE <= 2 * SLAB128 + SLAB64 && STG_TILE <= SLAB128 - SLAB64, "staging tiles must fit their hosts");
+__device__ __forceinline__ int stage_off(int m) { return m < 5 ? OFF_AR + m * STG_TILE : OFF_M2A + SLAB64; }
 struct Small {
     float h1[kN];        // cumulative log-decay of tokens 0..31
     float tot[kN];       // ... of the whole chunk
     float lam[kN];       // exp(tot)
-    uint64_t bar[4];
+    uint64_t bar[5];   // 0..3 product rounds, 4 staging tiles
     uint32_t nsm[2];
     uint32_t tmem;
 };
@@ -77,7 +83,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
-                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len) {
+                      __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
+                      const __grid_constant__ StreamMaps maps) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -92,7 +99,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tc::mbar_init(&sm.bar[i], 1);
+        for (int i = 0; i < 5; ++i) tc::mbar_init(&sm.bar[i], 1);
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(&sm.tmem, 256);
@@ -135,8 +142,18 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     const int tsub = tid >> 3, jb = tid & 7;                // staging unit: tokens 32q+tsub (q=0,1), channels 8jb..8jb+7
 
     int p = 0;
-    uint32_t par = 0;
+    uint32_t par = 0, spar = 0;   // phase parities of the product barriers and of the staging barrier
     uint8_t flag_ahead = (tid < 64 && tid < Tlen) ? new_starts[(size_t)bi * Tlen + tid] : 0;
+    // the 64 token rows from cp on of w, r, k, v, a, b into the staging tiles (thread 0; one tiled copy
+    // per stream).  Rows past the chunk arrive too and are ignored.
+    auto issue_stage = [&](int cp) {
+        if (tid == 0) {
+            tc::mbar_expect_tx(&sm.bar[4], (uint32_t)(6 * STG_TILE));
+#pragma unroll
+            for (int m = 0; m < 6; ++m) tc::tensor_load_2d(smem + stage_off(m), &maps.m[m], h * kN, bi * Tlen + cp, &sm.bar[4]);
+        }
+    };
+    issue_stage(0);
 #ifdef WKV_PROF
     long long prof_t_ = clock64();
 #endif
@@ -185,18 +202,17 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // ================= stage inputs (registers), log-decay into the scan buffer =================
         uint4 raw[2][5];   // r, k, v, a, b
         float lw[2][8];    // log2 of the decay: -exp(w) * log2(e)
+        if (!tc::mbar_wait(&sm.bar[4], spar)) failed = true;   // the rows of this chunk have landed
+        spar ^= 1u;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const int t = q * 32 + tsub;
             if (t < n) {
-                const size_t g = seq_base + (size_t)(p + t) * tok_stride + jb * 8;
+                const int o = t * (kN * 2) + jb * 16;
                 float wf[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(w + g)), wf);
-                raw[q][0] = __ldg(reinterpret_cast<const uint4*>(r + g));
-                raw[q][1] = __ldg(reinterpret_cast<const uint4*>(k + g));
-                raw[q][2] = __ldg(reinterpret_cast<const uint4*>(v + g));
-                raw[q][3] = __ldg(reinterpret_cast<const uint4*>(a + g));
-                raw[q][4] = __ldg(reinterpret_cast<const uint4*>(b + g));
+                unpack8(*reinterpret_cast<const uint4*>(smem + stage_off(0) + o), wf);
+#pragma unroll
+                for (int m = 0; m < 5; ++m) raw[q][m] = *reinterpret_cast<const uint4*>(smem + stage_off(m + 1) + o);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) lw[q][e] = -kLog2e * __expf(wf[e]);   // log2 of the decay
             } else {
@@ -207,12 +223,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
             *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
             *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
-            // pull the lines of the next 64 tokens towards L2 (one thread per 128-byte line)
-            if (jb == 0 && p + kC + t < Tlen) {
-                const size_t gn = seq_base + (size_t)(p + kC + t) * tok_stride;
-                prefetch_l2(w + gn); prefetch_l2(r + gn); prefetch_l2(k + gn);
-                prefetch_l2(v + gn); prefetch_l2(a + gn); prefetch_l2(b + gn);
-            }
         }
         __syncthreads();
         PROF_MARK(2);
@@ -355,6 +365,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             mma_k64(tbase + D1, kmaj128(sTP), mnmaj64(sG), ID_128x64_KM, false);
             tc::commit(&sm.bar[2]);
         }
+        // the rows of the next chunk start travelling: their tiles lie over buffers that are idle from
+        // here to the next chunk's operand stores (the inverse and the A_ak / P_rk product are done)
+        if (p1 < Tlen) issue_stage(p1);
         if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[2], par)) failed = true;
             tc::fence_after_sync();
@@ -412,10 +425,14 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     typedef __nv_bfloat16 bf;
     if (cudaFuncSetAttribute(wkv7_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
         return B200WKV_ELAUNCH;
+    StreamMaps maps;
+    const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]
+    if (!make_stream_maps(&maps, bases, 6, B, T, H)) return B200WKV_ELAUNCH;
     wkv7_chunk_fwd_kernel<<<B * H, 256, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
                                                           (bf*)y, (bf*)s_out, (float*)residual,
-                                                          residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr);
+                                                          residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
+                                                          maps);
     (void)dbg;
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }

@@ -90,11 +90,6 @@ __device__ long long g_prof_bwd[24];   // cycles per phase, summed over the chun
 #define PROF_MARK(i) do { } while (0)
 #endif
 
-// tensor maps of the seven streams w, r, k, v, a, b, dy viewed as [B*T tokens][H*64 channels]
-struct StreamMaps {
-    CUtensorMap m[7];
-};
-
 // four K=16 steps (64 deep) of D (+)= A B
 __device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, bool accumulate) {
 #pragma unroll
@@ -771,9 +766,8 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     int* status = wkv7_chunk_status_word();
     int BH = B * H;
     StreamMaps maps;
-    const void* bases[7] = {w, r, k, v, a, b, dy != nullptr ? dy : w};
-    for (int m = 0; m < 7; ++m)
-        if (!make_tmap_bf16_2d(&maps.m[m], bases[m], (uint64_t)B * T, (uint64_t)H * kN, kC, kN)) return B200WKV_ELAUNCH;
+    const void* bases[7] = {w, r, k, v, a, b, dy};   // maps[m]: the seven streams as [B*T tokens][H*64 channels]
+    if (!make_stream_maps(&maps, bases, dy != nullptr ? 7 : 6, B, T, H)) return B200WKV_ELAUNCH;
     // One CTA per SM (shared memory).  With more sequences than SMs the CTAs are persistent; when
     // the sequences do not divide evenly, each is cut into `seg` runs of blocks so that every CTA
     // gets the same number of units, and neighbouring CTAs pass the carry through global memory.
