@@ -69,7 +69,9 @@ int b200wkv_device_status(void);
  * (the counterpart of the reference's s_restore/sa_restore results,
  * rwkv7.py:363-364).  Pass NULL/0 for inference: nothing is saved then.  The
  * backward must be called with the same dtype and flags as the forward that
- * filled the buffer.
+ * filled the buffer, and it uses the tail of the buffer as scratch (carries
+ * passed between thread blocks), so the buffer must be writable and one
+ * buffer must not serve two backward calls that overlap on the GPU.
  */
 size_t b200wkv7_residual_bytes(int dtype, int B, int T, int H, int N);
 
