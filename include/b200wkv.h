@@ -82,6 +82,20 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N,
                  void* y, void* s_out,
                  void* residual, size_t residual_bytes, unsigned flags);
 
+/* One decoding step (T == 1) that updates the state IN PLACE where the caller keeps it.  jaxrwkv
+ * carries the state of a model as (layers, 2 + N, D) per sequence (default_state,
+ * src/jaxrwkv/rwkv7.py:175-180): rows 2.. of a layer are the (H, N, N) block of this operator
+ * (rwkv7.py:255, :260), so under a batch the blocks of one layer are `state_batch_stride` elements
+ * apart.  `state` points at the block of batch row 0; streams are (B, 1, H, N), y likewise.  No copy
+ * of the state is made on either side of the step.  `state` must be 16-byte aligned and the stride
+ * a multiple of 16 bytes (B200WKV_EUNSUPPORTED otherwise).  length == 0 leaves a row's state as it
+ * is; a start flag zeroes it before the token (as b200wkv7_fwd). */
+int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N,
+                          const void* w, const void* r, const void* k, const void* v,
+                          const void* a, const void* b,
+                          void* state, long long state_batch_stride,
+                          const uint32_t* length, const uint8_t* new_starts, void* y);
+
 /* Backward: cotangents dy (B,T,H,N) and ds_out (B,H,N,N) in, gradients of all six
  * streams and of the initial state out (the reference's result order is
  * gw, gr, gk, gv, ga, gb, gs — rwkv7.py:406).  dy or ds_out may be NULL (= zeros).

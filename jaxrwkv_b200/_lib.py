@@ -20,6 +20,7 @@ PROTOTYPES = {
     "b200wkv_device_status": (_I, []),
     "b200wkv7_residual_bytes": (_SZ, [_I, _I, _I, _I, _I]),
     "b200wkv7_fwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ, _U]),
+    "b200wkv7_step_inplace": (_I, [_P, _I, _I, _I, _I] + [_P] * 6 + [_P, ctypes.c_longlong, _P, _P, _P]),
     "b200wkv7_bwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ] + [_P] * 7 + [_U]),
     "b200wkv6_residual_bytes": (_SZ, [_I, _I, _I, _I, _I]),
     "b200wkv6_fwd": (_I, [_P, _I, _I, _I, _I, _I, _I] + [_P] * 8 + [_P, _P, _P, _SZ, _U]),

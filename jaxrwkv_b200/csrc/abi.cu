@@ -14,6 +14,9 @@ int wkv7_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w,
 int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
               const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
               void* s_out);
+int wkv7_step_stream(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
+                     const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+                     void* s_out, long long s_batch_stride);
 size_t wkv7_chunk_residual_bytes(int B, int T, int H);
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
@@ -185,6 +188,19 @@ int b200wkv4_bwd(void* stream, int dtype, int B, int T, int C, const void* w, co
     (void)flags;
     return wkv4_bwd((cudaStream_t)stream, dtype, B, T, C, w, u, k, v, gy, length, new_starts, gs_new, residual, gw, gu,
                     gk, gv, gs);
+}
+
+int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N, const void* w, const void* r, const void* k,
+                          const void* v, const void* a, const void* b, void* state, long long state_batch_stride,
+                          const uint32_t* length, const uint8_t* new_starts, void* y) {
+    int st = check_dims(dtype, B, 1, H, N);
+    if (st != B200WKV_OK) return st;
+    if (!w || !r || !k || !v || !a || !b || !state || !length || !new_starts || !y) return B200WKV_ENULL;
+    const long long esz = dtype == B200WKV_F32 ? 4 : 2;
+    if (state_batch_stride < (long long)H * N * N) return B200WKV_ESHAPE;
+    if ((reinterpret_cast<uintptr_t>(state) & 15u) != 0 || (state_batch_stride * esz) % 16 != 0) return B200WKV_EUNSUPPORTED;
+    return wkv7_step_stream((cudaStream_t)stream, dtype, B, H, w, r, k, v, a, b, state, length, new_starts, y, state,
+                            state_batch_stride);
 }
 
 static int check_shift(int dtype, int B, int T, int D, int M) {

@@ -86,7 +86,7 @@ wkv7_step_stream_kernel(int BH, int H, const T* __restrict__ w, const T* __restr
                         const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
                         const T* __restrict__ s0, const uint32_t* __restrict__ length,
                         const uint8_t* __restrict__ new_starts, T* __restrict__ y, T* __restrict__ s_out,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, long long s_batch_stride) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     StepSmem<T>& sm = *reinterpret_cast<StepSmem<T>*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -95,6 +95,9 @@ wkv7_step_stream_kernel(int BH, int H, const T* __restrict__ w, const T* __restr
     const int first = blockIdx.x, stride = gridDim.x;
     const int n_my = (BH - first + stride - 1) / stride;   // pairs first, first + stride, ...
     constexpr uint32_t kTileBytes = kStateElems * sizeof(T);
+    // element offset of the state of pair q: batch rows may be s_batch_stride elements apart (a state
+    // that lives inside a larger per-sequence container), heads of one row are contiguous
+    auto state_off = [&](int q) { return (size_t)(q / H) * (size_t)s_batch_stride + (size_t)(q % H) * kStateElems; };
     // threads 0..95 fetch the six vectors: stream vm, channels vc..vc+3
     const int vm = tid >> 4, vc = (tid & 15) * 4;
     const T* vsrc = vm == 0 ? w : vm == 1 ? r : vm == 2 ? k : vm == 3 ? v : vm == 4 ? a : b;
@@ -108,7 +111,7 @@ wkv7_step_stream_kernel(int BH, int H, const T* __restrict__ w, const T* __restr
     if (tid == 0) {
         for (int s = 0; s < kStages && s < n_my; ++s) {
             tc::mbar_expect_tx(&sm.full[s], kTileBytes);
-            tc::bulk_load(sm.stage[s], s0 + (size_t)(first + s * stride) * kStateElems, kTileBytes, &sm.full[s]);
+            tc::bulk_load(sm.stage[s], s0 + state_off(first + s * stride), kTileBytes, &sm.full[s]);
         }
     }
     if (tid < 96) {
@@ -134,15 +137,15 @@ wkv7_step_stream_kernel(int BH, int H, const T* __restrict__ w, const T* __restr
         __syncthreads();   // every thread holds its part of stage s; vec[it & 1] is complete
         if (tid == 0 && it + kStages < n_my) {
             tc::mbar_expect_tx(&sm.full[s], kTileBytes);
-            tc::bulk_load(sm.stage[s], s0 + (size_t)(bh + kStages * stride) * kStateElems, kTileBytes, &sm.full[s]);
+            tc::bulk_load(sm.stage[s], s0 + state_off(bh + kStages * stride), kTileBytes, &sm.full[s]);
         }
         if (more && tid < 96) {
             if (vm == 0) nx = make_float4(expf(-expf(nx.x)), expf(-expf(nx.y)), expf(-expf(nx.z)), expf(-expf(nx.w)));
             *reinterpret_cast<float4*>(&sm.vec[(it + 1) & 1][vm][vidx(vc)]) = nx;
         }
         const float (*vec)[kVecPitch] = sm.vec[it & 1];
-        T* out_a = s_out + ((size_t)bh * kN + ra) * kN;
-        T* out_b = s_out + ((size_t)bh * kN + rb) * kN;
+        T* out_a = s_out + state_off(bh) + (size_t)ra * kN;
+        T* out_b = s_out + state_off(bh) + (size_t)rb * kN;
         if (keep_input) {
             Own<T>::store(out_a, p, Sa);
             Own<T>::store(out_b, p, Sb);
@@ -194,7 +197,8 @@ wkv7_step_stream_kernel(int BH, int H, const T* __restrict__ w, const T* __restr
 
 template <typename T>
 int launch(cudaStream_t st, int B, int H, const void* w, const void* r, const void* k, const void* v, const void* a,
-           const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y, void* s_out) {
+           const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y, void* s_out,
+           long long s_batch_stride) {
     static int sm_count = 0;
     if (sm_count == 0) {
         int dev = 0;
@@ -210,18 +214,20 @@ int launch(cudaStream_t st, int B, int H, const void* w, const void* r, const vo
     const int BH = B * H;
     const int grid = BH < sm_count * per_sm ? BH : sm_count * per_sm;   // one wave: every CTA resident
     kern<<<grid, 256, smem, st>>>(BH, H, (const T*)w, (const T*)r, (const T*)k, (const T*)v, (const T*)a, (const T*)b,
-                                  (const T*)s0, length, ns, (T*)y, (T*)s_out, wkv7_chunk_status_word());
+                                  (const T*)s0, length, ns, (T*)y, (T*)s_out, wkv7_chunk_status_word(), s_batch_stride);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
 }  // namespace
 
-// Requires s0 and s_out 16-byte aligned (the bulk copies and the vector stores); the caller checks.
+// Requires s0 and s_out 16-byte aligned (the bulk copies and the vector stores) and a batch stride
+// that keeps every row aligned; the caller checks.  s_out may be s0 (update in place): a pair's state
+// is read into the ring before its own write-back and no other pair touches it.
 int wkv7_step_stream(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
                      const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
-                     void* s_out) {
-    if (dtype == B200WKV_F32) return launch<float>(st, B, H, w, r, k, v, a, b, s0, length, ns, y, s_out);
-    return launch<__nv_bfloat16>(st, B, H, w, r, k, v, a, b, s0, length, ns, y, s_out);
+                     void* s_out, long long s_batch_stride) {
+    if (dtype == B200WKV_F32) return launch<float>(st, B, H, w, r, k, v, a, b, s0, length, ns, y, s_out, s_batch_stride);
+    return launch<__nv_bfloat16>(st, B, H, w, r, k, v, a, b, s0, length, ns, y, s_out, s_batch_stride);
 }
 
 }  // namespace b200wkv

@@ -206,6 +206,37 @@ def wkv7_step(r, w, k, v, a, b, s, new_starts=None, length=None):
     return new_s, out.reshape(shp)
 
 
+def wkv7_step_packed(r, w, k, v, a, b, state, layer, new_starts=None, length=None):
+    """One decoding step on the model's packed state, updated in place.
+
+    ``state`` is jaxrwkv's per-sequence container under a batch, ``(B, L, 2 + N, D)`` with
+    ``D = H * N`` (``default_state``, rwkv7.py:175-180); rows ``2:`` of layer ``layer`` are this
+    operator's ``(H, N, N)`` block (rwkv7.py:255, :260).  The kernel reads and writes that block
+    where it lies: no slice is copied out or back.  Returns ``out`` shaped like ``r``.
+    """
+    lib = _lib.load()
+    shp = r.shape
+    B, H, N = shp[0], shp[-2], shp[-1]
+    Bs, L, rows, D = state.shape
+    if not (Bs == B and rows == 2 + N and D == H * N and state.is_contiguous() and state.dtype == r.dtype):
+        raise _lib.B200WKVError("wkv7_step_packed: state must be a contiguous (B, L, 2+N, H*N) tensor of the streams' dtype")
+    flat = [x.reshape(B, 1, H, N).contiguous() for x in (r, w, k, v, a, b)]
+    code = _check_inputs(*flat, state)
+    key = (B, r.device)
+    if key not in _STEP_FLAGS:
+        _STEP_FLAGS[key] = (torch.zeros(B, 1, dtype=torch.uint8, device=r.device),
+                            torch.ones(B, dtype=torch.int32, device=r.device))
+    new_starts = _STEP_FLAGS[key][0] if new_starts is None else new_starts.to(device=r.device, dtype=torch.uint8).reshape(B, 1).contiguous()
+    length = _STEP_FLAGS[key][1] if length is None else length.to(device=r.device, dtype=torch.int32).contiguous()
+    out = torch.empty_like(flat[0])
+    block = state[:, layer, 2:]                 # (B, N, D) view: B blocks of H*N*N elements, L*(2+N)*D apart
+    rr, ww, kk, vv, aa, bb = flat
+    _lib.check(lib.b200wkv7_step_inplace(_stream(), code, B, H, N, _ptr(ww), _ptr(rr), _ptr(kk), _ptr(vv), _ptr(aa),
+                                         _ptr(bb), block.data_ptr(), state.stride(0), _ptr(length), _ptr(new_starts),
+                                         _ptr(out)))
+    return out.reshape(shp)
+
+
 def wkv7_cuda(r, w, k, v, a, b, s, length, new_starts):
     """Differentiable WKV-7 operator (rwkv7.py:442-446).  Tensors are (..., T, H, N) with any
     number of leading batch axes, the state (..., H, N, N); ``length`` and ``new_starts`` may

@@ -436,6 +436,32 @@ def test_decode_step_many_pairs_ring_wraps(dtype):
     assert rel_err(npf(s3), s2.cpu().numpy()) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_step_on_packed_state_in_place(dtype):
+    """The step that updates the (H, N, N) block inside the model's packed (B, L, 2+N, D) state where
+    it lies equals the step on a copied-out block, and touches nothing else in the container."""
+    B, H, L, N = 6, 5, 3, 64
+    g = torch.Generator(device="cuda").manual_seed(17)
+    shp = (B, 1, H, N)
+    r, k, v = (torch.randn(shp, device="cuda", generator=g).to(dtype) for _ in range(3))
+    w = (-0.5 - torch.nn.functional.softplus(torch.randn(shp, device="cuda", generator=g))).to(dtype)
+    kk = torch.nn.functional.normalize(torch.randn(shp, device="cuda", generator=g), dim=-1)
+    a, b = (-kk).to(dtype), (kk * torch.rand(shp, device="cuda", generator=g)).to(dtype)
+    state = (0.5 * torch.randn(B, L, 2 + N, H * N, device="cuda", generator=g)).to(dtype)
+    ns = torch.zeros(B, 1, dtype=torch.uint8, device="cuda"); ns[2] = 1
+    length = torch.ones(B, dtype=torch.int32, device="cuda"); length[4] = 0
+    layer = 1
+    before = state.clone()
+    # the reference reshapes state[1:] (N, H*N) to (H, N, N) as a raw reshape (rwkv7.py:255)
+    s_in = before[:, layer, 2:].reshape(B, H, N, N)
+    s_ref, y_ref = rwkv7.wkv7_step(r, w, k, v, a, b, s_in, new_starts=ns, length=length)
+    y = rwkv7.wkv7_step_packed(r, w, k, v, a, b, state, layer, new_starts=ns, length=length)
+    assert torch.equal(y, y_ref)
+    assert torch.equal(state[:, layer, 2:].reshape(B, H, N, N), s_ref)
+    untouched = torch.ones(L, 2 + N, dtype=torch.bool); untouched[layer, 2:] = False
+    assert torch.equal(state[:, untouched], before[:, untouched])
+
+
 def test_no_bounded_wait_ran_out_during_the_suite():
     """Every mbarrier wait in the tensor-core kernels is bounded and records a failure in a device
     word; after the tensor-core tests above that word must still be clear."""
