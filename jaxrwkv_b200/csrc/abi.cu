@@ -52,7 +52,7 @@ static int check_dims(int dtype, int B, int T, int H, int N) {
     if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
     if (B < 1 || T < 1 || H < 1 || N != kN) return B200WKV_ESHAPE;
     // element counts are indexed with size_t; the grid is B*H blocks
-    if ((long long)B * H > 2147483647LL) return B200WKV_ESHAPE;
+    if ((long long)B * H > 2147483647LL || (long long)B * T > 2147483647LL) return B200WKV_ESHAPE;   // token rows index tensor maps
     return B200WKV_OK;
 }
 }  // namespace b200wkv
