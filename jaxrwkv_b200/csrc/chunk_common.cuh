@@ -26,8 +26,17 @@ constexpr int kHandoffFloats = kN * kN + kN;
 inline size_t chunk_states_floats(int B, int T, int H) {
     return (size_t)B * H * ((size_t)((T + kC - 1) / kC) + 1) * kN * kN;
 }
-inline size_t chunk_residual_floats(int B, int T, int H) {
+//   [B*H][ceil(T/64)][5 slabs]  for every 64-token block that the forward walked as ONE chunk: the bf16
+//                               operand slabs T = (I - A_ab)^-1, A_ak, P_rb, P_rk and sa exactly as the forward
+//                               used them, so the backward loads them instead of recomputing them
+constexpr int kSavedSlabs = 5;   // order: T, A_ak, P_rb, P_rk, sa (64-row slabs)
+constexpr int SAVED_T = 0, SAVED_AAK = 1, SAVED_PRB = 2, SAVED_PRK = 3, SAVED_SA = 4;
+constexpr size_t kSavedBytes = (size_t)kSavedSlabs * SLAB64;
+inline size_t chunk_saved_offset_floats(int B, int T, int H) {
     return chunk_states_floats(B, T, H) + (size_t)kHandoffSlots * (kHandoffFloats + 1);
+}
+inline size_t chunk_residual_floats(int B, int T, int H) {
+    return chunk_saved_offset_floats(B, T, H) + (size_t)B * H * ((T + kC - 1) / kC) * (kSavedBytes / sizeof(float));
 }
 
 // Host side of the split: grid size and segments per sequence for `chains` sequences of `n_blk`
@@ -197,14 +206,18 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
 }
 
 // bf16 copy of a 64x64 fp32 matrix (pitch LF_PITCH) into rows 0..63 of an operand slab
+// `copy` (may be null): a second destination in global memory, laid out as a 64-row slab (column blocks of CB64)
 template <int NT>
-__device__ __forceinline__ void fp32_to_slab64(const float* __restrict__ X, unsigned char* slab, int cb, int tid) {
+__device__ __forceinline__ void fp32_to_slab64(const float* __restrict__ X, unsigned char* slab, int cb, int tid,
+                                               unsigned char* copy = nullptr) {
     for (int idx = tid; idx < 512; idx += NT) {
         const int row = idx & 63, blk = idx >> 6;
         float f[8];
         *reinterpret_cast<float4*>(&f[0]) = *reinterpret_cast<const float4*>(&X[row * LF_PITCH + blk * 8]);
         *reinterpret_cast<float4*>(&f[4]) = *reinterpret_cast<const float4*>(&X[row * LF_PITCH + blk * 8 + 4]);
-        slab_store(slab, cb, row, blk, pack8(f));
+        const uint4 packed = pack8(f);
+        slab_store(slab, cb, row, blk, packed);
+        if (copy != nullptr) *reinterpret_cast<uint4*>(copy + blk * CB64 + row * 16) = packed;
     }
 }
 

@@ -84,7 +84,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
                       __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
-                      const __grid_constant__ StreamMaps maps) {
+                      const __grid_constant__ StreamMaps maps, unsigned char* __restrict__ saved) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -198,6 +198,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if ((mask >> 1) != 0) p1 = p + __ffsll((long long)(mask >> 1));
         if (L > p && L < p1) p1 = L;
         const int n = p1 - p;
+        // a block walked as one full chunk leaves its operand slabs T, A_ak, P_rb, P_rk, sa for the backward
+        unsigned char* const keep = (saved != nullptr && n == kC && (p & (kC - 1)) == 0)
+                                        ? saved + ((size_t)bh * nBlk + (p >> 6)) * kSavedBytes : nullptr;
         PROF_MARK(1);
         // ================= stage inputs (registers), log-decay into the scan buffer =================
         uint4 raw[2][5];   // r, k, v, a, b
@@ -328,8 +331,14 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 for (int s = 0; s < 64; ++s) d[s] = (s < lim) ? d[s] : 0.f;
                 // A_ak -> M2A rows 0..63, P_rk -> M2A rows 64..127, P_rb -> TP rows 64..127
                 unsigned char* dst = smem + ((hsel == 1) ? OFF_M2A : OFF_TP);
+                unsigned char* kdst = keep == nullptr ? nullptr
+                                      : keep + (size_t)((row < 64) ? SAVED_AAK : (hsel == 1 ? SAVED_PRK : SAVED_PRB)) * SLAB64 + t * 16;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) slab_store(dst, CB128, row, c, pack8(&d[c * 8]));
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 packed = pack8(&d[c * 8]);
+                    slab_store(dst, CB128, row, c, packed);
+                    if (kdst != nullptr) *reinterpret_cast<uint4*>(kdst + c * CB64) = packed;
+                }
             }
         }
         tc::fence_async_smem();
@@ -344,7 +353,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         PROF_MARK(8);
         tri_inverse_64<256>(lf, xinv, scr, tid);
-        fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid);
+        fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid, keep == nullptr ? nullptr : keep + (size_t)SAVED_T * SLAB64);
         PROF_MARK(9);
         if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
@@ -375,7 +384,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::tmem_ld32(lane_addr + D1 + hsel * 32, sa);
             tc::tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) slab_store(smem + OFF_SA, CB64, row, hsel * 4 + c, pack8(&sa[c * 8]));
+            for (int c = 0; c < 4; ++c) {
+                const uint4 packed = pack8(&sa[c * 8]);
+                slab_store(smem + OFF_SA, CB64, row, hsel * 4 + c, packed);
+                if (keep != nullptr) *reinterpret_cast<uint4*>(keep + (size_t)SAVED_SA * SLAB64 + (hsel * 4 + c) * CB64 + row * 16) = packed;
+            }
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
@@ -432,7 +445,8 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
                                                           (bf*)y, (bf*)s_out, (float*)residual,
                                                           residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
-                                                          maps);
+                                                          maps,
+                                                          residual ? (unsigned char*)((float*)residual + chunk_saved_offset_floats(B, T, H)) : nullptr);
     (void)dbg;
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }

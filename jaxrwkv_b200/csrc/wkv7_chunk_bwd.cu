@@ -66,7 +66,7 @@ struct Small {
     float d_in[kN];        // D carried from the chunk processed before (later in time)
     float d_part[2][kN];   // partial column sums of the new anchor
     float seg[4][kN];      // per-16-token totals of the decay-gradient scan
-    uint64_t bar[6];       // 0..4 product rounds, 5 staging tiles
+    uint64_t bar[7];       // 0..4 product rounds, 5 staging tiles, 6 operand slabs saved by the forward
     uint32_t nsm[2];       // chunk starts inside the current 64-token block
     uint32_t nsf[2];       // start flags inside the current block
     uint32_t tmem;
@@ -106,7 +106,8 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ dr, __nv_bfloat16* __restrict__ dk,
                       __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
                       __nv_bfloat16* __restrict__ ds0, int* __restrict__ status, int BH, int SEG,
-                      float* __restrict__ carry, int* __restrict__ carry_flag, const __grid_constant__ StreamMaps maps) {
+                      float* __restrict__ carry, int* __restrict__ carry_flag, const __grid_constant__ StreamMaps maps,
+                      const unsigned char* __restrict__ saved) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -124,7 +125,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 6; ++i) tc::mbar_init(&sm.bar[i], 1);
+        for (int i = 0; i < 7; ++i) tc::mbar_init(&sm.bar[i], 1);
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(&sm.tmem, 512);
@@ -152,7 +153,8 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     const int tsub = tid >> 3, jb = tid & 7;   // staging unit: tokens 32q + tsub (q = 0,1), channels 8jb..8jb+7
     const int si = tid & 63, scq = tid >> 6;   // state element ownership: row si, columns 16scq..16scq+15
-    uint32_t par = 0, spar = 0;   // phase parities of the product barriers and of the staging barrier
+    // phase parities: product rounds 1..4 (every chunk), round 0 (recomputing chunks only), staging tiles, saved slabs
+    uint32_t par = 0, par0 = 0, spar = 0, lpar = 0;
 #ifdef WKV_PROF
     long long prof_t_ = clock64();
 #endif
@@ -164,14 +166,19 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     bool reset_here = false;
     uint4 raw[2][6];   // r, k, v, a, b, dy
     uint4 wraw[2];     // raw log-log decay
+    uint8_t flag_ahead = 0;   // threads 0..63: the start flag of their token in the block planned next
+    auto fetch_flags = [&](int b) {
+        if (tid < 64 && b >= 0 && b * kC + tid < Tlen) flag_ahead = new_starts[(size_t)bi * Tlen + b * kC + tid];
+    };
     auto plan_block = [&](int b) {
-        // chunk starts inside block b: its first token, every start flag, and `length`
+        // chunk starts inside block b: its first token, every start flag, and `length`.  The flag bytes
+        // were requested one block earlier (fetch_flags), so no global load sits in front of the ballots.
         bs = b * kC;
         be = min(bs + kC, Tlen);
         __syncthreads();
         if (tid < 64) {
             const int pos = bs + tid;
-            const bool flag = (pos < be) && (new_starts[(size_t)bi * Tlen + pos] != 0);
+            const bool flag = (pos < be) && (flag_ahead != 0);
             const bool f = (pos < be) && (tid == 0 || flag || pos == L);
             const uint32_t m = __ballot_sync(0xffffffffu, f), mf = __ballot_sync(0xffffffffu, flag);
             if (lane == 0) { sm.nsm[warp] = m; sm.nsf[warp] = mf; }
@@ -179,6 +186,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             // the saved state of the block processed after this one: one 128-byte line per thread towards L2
             prefetch_l2(ckpt + ((size_t)bh * nBlk + b - 1) * kN * kN + (tid - 64) * 32);
         }
+        fetch_flags(b - 1);
         __syncthreads();
         cmask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
         fmask = (uint64_t)sm.nsf[0] | ((uint64_t)sm.nsf[1] << 32);
@@ -191,10 +199,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         reset_here = ((fmask >> (p - bs)) & 1ull) != 0;
     };
     // the 64 token rows from cp on of the seven streams into the staging tiles: one tiled copy of
-    // 64 x 128 bytes per stream, all issued by thread 0.  Rows past the chunk arrive too and are ignored.
+    // 64 x 128 bytes per stream, all issued by one thread.  Rows past the chunk arrive too and are ignored.
     const int n_streams = (dy != nullptr) ? 7 : 6;
     auto issue_stage = [&](int cp) {
-        if (tid == 0) {
+        if (tid == 32) {   // not the thread that issues the products
             tc::mbar_expect_tx(&sm.bar[5], (uint32_t)(n_streams * STG_TILE));
             const int x = (bh % H) * kN, y = bi * Tlen + cp;
 #pragma unroll
@@ -221,6 +229,28 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
     };
+    // A 64-token block that the forward walked as one chunk has its operand slabs T, A_ak, P_rb, P_rk and sa
+    // in the residual: the backward copies them in instead of recomputing them (no Gram product, no inverse).
+    // P_rb|P_rk and sa can start as soon as the fifth product round of the chunk before has completed;
+    // T|A_ak lie under staging tiles and follow once take_stage has emptied those.
+    auto is_saved = [&](int cp, int cn) { return cn == kC && (cp & (kC - 1)) == 0; };
+    auto issue_saved_late = [&](int cp) {
+        if (tid == 32) {
+            const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
+            tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(4 * SLAB64 + kC * kN * 2));
+            tc::bulk_load(smem + OFF_PRB, src + SAVED_PRB * SLAB64, 2 * SLAB64, &sm.bar[6]);
+#pragma unroll
+            for (int c = 0; c < 8; ++c)   // sa: rows 64..127 of the [V ; sa] slab, one column block at a time
+                tc::bulk_load(smem + OFF_VSA + c * CB128 + 64 * 16, src + SAVED_SA * SLAB64 + c * CB64, 64 * 16, &sm.bar[6]);
+        }
+    };
+    auto issue_saved_early = [&](int cp) {
+        if (tid == 32) {
+            const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
+            tc::bulk_load(smem + OFF_TINV, src + SAVED_T * SLAB64, 2 * SLAB64, &sm.bar[6]);
+        }
+    };
+    bool loaded_next = false;
     for (int order = 0; order < n_runs; ++order) {
     const RunPlan run = run_at(unit_lo, unit_hi, SEG, order);
     bh = run.chain;
@@ -260,14 +290,21 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if (tid < 64) sm.d_in[tid] = __ldcg(src + kN * kN + tid);
     }
     blk = blk_hi - 1;
+    fetch_flags(blk);
     plan_block(blk);   // begins and ends with a barrier: dsf and d_in are in place afterwards
     p1 = be;
     plan_chunk(p1);
     tc::fence_async_smem();   // the tiles' hosts were last written by ordinary stores
     __syncthreads();
     issue_stage(p);
+    loaded_next = is_saved(p, n);
+    if (loaded_next) issue_saved_late(p);
+#ifdef WKV_PROF
+    prof_t_ = clock64();
+#endif
     while (true) {
         {
+            const bool cur_loaded = loaded_next;
             take_stage();
             // ---------------- cotangent of the returned state enters at position `length` ----------------
             if (p1 == L && ds_out != nullptr) {
@@ -298,6 +335,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
             PROF_MARK(1);
             __syncthreads();
+            if (cur_loaded) issue_saved_early(p);   // every thread has emptied the staging tiles over T | A_ak
             if (tid < 128) {
                 const int j = tid & 63, half = tid >> 6;
                 float run = 0.f;
@@ -371,6 +409,12 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_before_sync();
             __syncthreads();
             PROF_MARK(4);
+            if (cur_loaded) {
+                // T, A_ak, P_rb, P_rk and sa of this chunk come from the forward
+                if (!tc::mbar_wait(&sm.bar[6], lpar)) failed = true;
+                lpar ^= 1u;
+                PROF_MARK(5);
+            } else {
             // ================= R1: Gram blocks, A~ S0^T =================
             if (tid == 0) {
                 tc::fence_after_sync();
@@ -378,7 +422,8 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_G, kmaj128(sAR), kmaj64(sS0), ID_KK, false);
                 tc::commit(&sm.bar[0]);
             }
-            if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
+            if (!tc::mbar_wait(&sm.bar[0], par0)) failed = true;
+            par0 ^= 1u;
             tc::fence_after_sync();
             PROF_MARK(5);
             {
@@ -405,31 +450,38 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
+            }   // recomputing chunk
             PROF_MARK(6);
             // ================= R2: G += A_ak V ; [Gd ; dVpart] = [B~;K~] dSL^T + [P_rb|P_rk]^T dY ; inverse =================
             if (tid == 0) {
                 tc::fence_after_sync();
-                mma_k64(tbase + T_G, kmaj64(sAAK), mnmaj128(sVSA), ID_KM, true);
+                if (!cur_loaded) mma_k64(tbase + T_G, kmaj64(sAAK), mnmaj128(sVSA), ID_KM, true);
                 mma_k64(tbase + T_GD, kmaj128(sBK), kmaj64(sDSL), ID_KK, false);
                 mma_k64(tbase + T_GD, mnmaj64(sPRB), mnmaj128(sDD), ID_MM, true);
                 tc::commit(&sm.bar[1]);
             }
             PROF_MARK(7);
-            tri_inverse_64<256>(lf, reinterpret_cast<float*>(smem + OFF_XINV), reinterpret_cast<float*>(smem + OFF_SCR), tid);
-            fp32_to_slab64<256>(reinterpret_cast<const float*>(smem + OFF_XINV), smem + OFF_TINV, CB64, tid);
+            if (!cur_loaded) {
+                tri_inverse_64<256>(lf, reinterpret_cast<float*>(smem + OFF_XINV), reinterpret_cast<float*>(smem + OFF_SCR), tid);
+                fp32_to_slab64<256>(reinterpret_cast<const float*>(smem + OFF_XINV), smem + OFF_TINV, CB64, tid);
+            }
             PROF_MARK(8);
             if (quad < 2) {
                 if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
                 tc::fence_after_sync();
-                float g[32], gd[32];
-                tc::tmem_ld32(lane_addr + T_G + hsel * 32, g);
+                float gd[32];
                 tc::tmem_ld32(lane_addr + T_GD + hsel * 32, gd);
-                tc::tmem_wait_ld();
+                if (!cur_loaded) {
+                    float g[32];
+                    tc::tmem_ld32(lane_addr + T_G + hsel * 32, g);
+                    tc::tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    slab_store(smem + OFF_G, CB64, row, hsel * 4 + c, pack8(&g[c * 8]));
-                    slab_store(smem + OFF_GD, CB64, row, hsel * 4 + c, pack8(&gd[c * 8]));
+                    for (int c = 0; c < 4; ++c) slab_store(smem + OFF_G, CB64, row, hsel * 4 + c, pack8(&g[c * 8]));
+                } else {
+                    tc::tmem_wait_ld();
                 }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) slab_store(smem + OFF_GD, CB64, row, hsel * 4 + c, pack8(&gd[c * 8]));
             }
             tc::fence_async_smem();
             tc::fence_before_sync();
@@ -438,22 +490,26 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             // ================= R3: sa = T G ; dsa = T^T Gd =================
             if (tid == 0) {
                 tc::fence_after_sync();
-                mma_k64(tbase + T_SA, kmaj64(sTINV), mnmaj64(sG), ID_KM, false);
+                if (!cur_loaded) mma_k64(tbase + T_SA, kmaj64(sTINV), mnmaj64(sG), ID_KM, false);
                 mma_k64(tbase + T_DSA, mnmaj64(sTINV), mnmaj64(sGD), ID_MM, false);
                 tc::commit(&sm.bar[2]);
             }
             if (quad < 2) {
                 if (!tc::mbar_wait(&sm.bar[2], par)) failed = true;
                 tc::fence_after_sync();
-                float x[32], z[32];
-                tc::tmem_ld32(lane_addr + T_SA + hsel * 32, x);
+                float z[32];
                 tc::tmem_ld32(lane_addr + T_DSA + hsel * 32, z);
-                tc::tmem_wait_ld();
+                if (!cur_loaded) {
+                    float x[32];
+                    tc::tmem_ld32(lane_addr + T_SA + hsel * 32, x);
+                    tc::tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    slab_store(smem + OFF_VSA, CB128, 64 + row, hsel * 4 + c, pack8(&x[c * 8]));
-                    slab_store(smem + OFF_DD, CB128, 64 + row, hsel * 4 + c, pack8(&z[c * 8]));
+                    for (int c = 0; c < 4; ++c) slab_store(smem + OFF_VSA, CB128, 64 + row, hsel * 4 + c, pack8(&x[c * 8]));
+                } else {
+                    tc::tmem_wait_ld();
                 }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) slab_store(smem + OFF_DD, CB128, 64 + row, hsel * 4 + c, pack8(&z[c * 8]));
             }
             tc::fence_async_smem();
             tc::fence_before_sync();
@@ -479,6 +535,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 if (cur_p == bs) plan_block(--blk);
                 plan_chunk(cur_p);
             }
+            loaded_next = has_next && is_saved(p, n);
             {
                 const int t = row & 63;
                 float d[64];
@@ -591,6 +648,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
             if (!tc::mbar_wait(&sm.bar[4], par)) failed = true;
             tc::fence_after_sync();
+            if (loaded_next) issue_saved_late(p);   // P_rb | P_rk and sa of the next chunk: their hosts are idle now
             PROF_MARK(14);
             float p3[32];   // a_t da_t for the rows that own da
             {
@@ -760,6 +818,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     // the tail of the buffer is scratch for carries between CTAs (see chunk_residual_floats)
     float* carry = const_cast<float*>(ck) + chunk_states_floats(B, T, H);
     int* carry_flag = reinterpret_cast<int*>(carry + (size_t)kHandoffSlots * kHandoffFloats);
+    const unsigned char* saved = reinterpret_cast<const unsigned char*>(ck + chunk_saved_offset_floats(B, T, H));
     const bf *pw = (const bf*)w, *pr = (const bf*)r, *pk = (const bf*)k, *pv = (const bf*)v, *pa = (const bf*)a, *pb = (const bf*)b;
     const bf *pdy = (const bf*)dy, *pds = (const bf*)ds_out;
     bf *gw = (bf*)dw, *gr = (bf*)dr, *gk = (bf*)dk, *gv = (bf*)dv, *ga = (bf*)da, *gb = (bf*)db, *gs = (bf*)ds0;
@@ -776,7 +835,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
         if (cudaMemsetAsync(carry_flag, 0, (size_t)kHandoffSlots * sizeof(int), st) != cudaSuccess) return B200WKV_ELAUNCH;
         int Tl = T, Hl = H, seg = plan.seg;
         void* args[] = {&Tl, &Hl, &pw, &pr, &pk, &pv, &pa, &pb, &length, &ns, &pdy, &pds, &ck, &sl, &gw, &gr, &gk, &gv, &ga,
-                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps};
+                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps, &saved};
         // cooperative launch: the runtime guarantees that all CTAs are resident at once, which the
         // carry hand-over relies on; if it refuses, fall through to one CTA per sequence
         if (cudaLaunchCooperativeKernel((const void*)wkv7_chunk_bwd_kernel, dim3(plan.grid), dim3(256), args, SMEM_BYTES, st) ==
@@ -786,7 +845,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     }
     wkv7_chunk_bwd_kernel<<<plan.seg > 1 ? BH : plan.grid, 256, SMEM_BYTES, st>>>(T, H, pw, pr, pk, pv, pa, pb, length, ns, pdy, pds, ck,
                                                                                sl, gw, gr, gk, gv, ga, gb, gs, status, BH, 1,
-                                                                               carry, carry_flag, maps);
+                                                                               carry, carry_flag, maps, saved);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
