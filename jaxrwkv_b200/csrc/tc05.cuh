@@ -96,6 +96,10 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// Asks for a contiguous range of global memory to be brought into L2 (no destination, no completion)
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(src_gmem)), "r"(bytes) : "memory");
+}
 // Tiled copy of one box of a 2-D tensor map into this CTA's shared memory.  x (innermost coordinate)
 // times the element size must be a multiple of 16 bytes; the destination 128-byte aligned.
 __device__ __forceinline__ void tensor_load_2d(void* dst_smem, const void* tmap, int x, int y, uint64_t* bar) {

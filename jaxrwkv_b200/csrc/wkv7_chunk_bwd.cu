@@ -64,7 +64,7 @@ struct Small {
     float tot[kN];
     float lam[kN];
     float d_in[kN];        // D carried from the chunk processed before (later in time)
-    float d_part[2][kN];   // partial column sums of the new anchor
+    float d_part[4][kN];   // partial column sums of the new anchor (16 rows each)
     float seg[4][kN];      // per-16-token totals of the decay-gradient scan
     uint64_t bar[7];       // 0..4 product rounds, 5 staging tiles, 6 operand slabs saved by the forward
     uint32_t nsm[2];       // chunk starts inside the current 64-token block
@@ -239,6 +239,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
             tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(4 * SLAB64 + kC * kN * 2));
             tc::bulk_load(smem + OFF_PRB, src + SAVED_PRB * SLAB64, 2 * SLAB64, &sm.bar[6]);
+            tc::bulk_prefetch_l2(src + SAVED_T * SLAB64, 2 * SLAB64);   // copied in later, from L2 then
 #pragma unroll
             for (int c = 0; c < 8; ++c)   // sa: rows 64..127 of the [V ; sa] slab, one column block at a time
                 tc::bulk_load(smem + OFF_VSA + c * CB128 + 64 * 16, src + SAVED_SA * SLAB64 + c * CB64, 64 * 16, &sm.bar[6]);
@@ -559,11 +560,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
                     for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&x[c * 8]);
                 }
-            } else {           // state-gradient carry and its exact anchor for the decay gradient
+            } else {           // state-gradient carry (fp32, shared memory): dS0 = dS diag(L_C) + dsa^T A~ + dY^T R~
                 float x[32];
                 tc::tmem_ld32(lane_addr + T_TMP + hsel * 32, x);
                 tc::tmem_wait_ld();
-                float pr[32];
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4) {
                     const int c = hsel * 32 + c4 * 4;
@@ -572,27 +572,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     old.x = fmaf(old.x, l4.x, x[c4 * 4 + 0]); old.y = fmaf(old.y, l4.y, x[c4 * 4 + 1]);
                     old.z = fmaf(old.z, l4.z, x[c4 * 4 + 2]); old.w = fmaf(old.w, l4.w, x[c4 * 4 + 3]);
                     *reinterpret_cast<float4*>(&dsf[row * LF_PITCH + c]) = old;
-                    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (s0src != nullptr) s4 = *reinterpret_cast<const float4*>(s0src + row * kN + c);
-                    pr[c4 * 4 + 0] = old.x * s4.x; pr[c4 * 4 + 1] = old.y * s4.y;
-                    pr[c4 * 4 + 2] = old.z * s4.z; pr[c4 * 4 + 3] = old.w * s4.w;
                 }
-                // column sums over the 32 rows of this warp: fold halves, lane l ends with column l
-#pragma unroll
-                for (int sh = 16; sh >= 1; sh >>= 1) {
-#pragma unroll
-                    for (int e = 0; e < sh; ++e) {
-                        const bool up = (lane & sh) != 0;
-                        const float send = up ? pr[e] : pr[e + sh];
-                        const float keep = up ? pr[e + sh] : pr[e];
-                        pr[e] = keep + __shfl_xor_sync(0xffffffffu, send, sh);
-                    }
-                }
-                // after the folds lane l holds the sum for column bitreverse-free index: see below
-                int col = 0;
-#pragma unroll
-                for (int sh = 16; sh >= 1; sh >>= 1) col += (lane & sh) ? sh : 0;
-                sm.d_part[quad][hsel * 32 + col] = pr[0];
             }
             tc::fence_async_smem();
             tc::fence_before_sync();
@@ -612,6 +592,20 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             // the rows of the next chunk (earlier in time) start travelling while the products run: their
             // tiles lie over buffers that the fourth round was the last to read
             if (has_next) issue_stage(p);
+            // exact anchor of the decay gradient for the chunk before: D = column sums of dS0 * S0 in fp32, by all
+            // threads (16 rows each) while the products run; the order of the additions is fixed
+            {
+                const int c = tid & 63, rq = tid >> 6;
+                float acc = 0.f;
+                if (s0src != nullptr) {
+#pragma unroll 8
+                    for (int rr = 0; rr < 16; ++rr) {
+                        const int r0 = rq * 16 + rr;
+                        acc = fmaf(dsf[r0 * LF_PITCH + c], __ldg(s0src + r0 * kN + c), acc);
+                    }
+                }
+                sm.d_part[rq][c] = acc;
+            }
             PROF_MARK(13);
             // everything of the epilogue that does not depend on the products runs while they execute:
             // decay factors of this row and the operand rows it pairs with (kept packed)
@@ -724,7 +718,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 __syncthreads();
                 // carry for the previous chunk: the exact anchor, or zero across a start flag
-                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
+                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : ((sm.d_part[0][tid] + sm.d_part[1][tid]) + (sm.d_part[2][tid] + sm.d_part[3][tid]));
                 __syncthreads();
                 if (row >= 64 && t < cur_n) {
                     float o[32];
