@@ -52,6 +52,14 @@ int b200wkv_abi_version(void);
  * synchronises the device, so it is not for the hot path.  Returns -1 if the CUDA runtime fails. */
 int b200wkv_device_status(void);
 
+/* Diagnostics of the work split used by the tensor-core backward (no GPU needed; for tests).
+ * split_plan: grid size and segments per sequence chosen for `chains` = B*H sequences of `n_blk`
+ * 64-token blocks with `per_sm` resident thread blocks per SM.  runs: the pieces thread block `cta` of
+ * `grid` walks, in walking order, as (sequence, first segment, one-past-last segment) triples written to
+ * `runs` (at most `capacity` of them); returns their number. */
+int b200wkv_debug_split_plan(int chains, int n_blk, int per_sm, int* grid, int* seg);
+int b200wkv_debug_runs(int chains, int seg, int grid, int cta, int* runs, int capacity);
+
 /* ---------------------------------------------------------------- RWKV-7 ----
  * Replaces the XLA custom calls "wkv7-fwd-{fp32,bf16}" / "wkv7-bwd-{fp32,bf16}"
  * that jaxrwkv binds at src/jaxrwkv/rwkv7.py:372-375 and :406-408 (handlers

@@ -18,6 +18,8 @@ PROTOTYPES = {
     "b200wkv_strerror": (ctypes.c_char_p, [_I]),
     "b200wkv_abi_version": (_I, []),
     "b200wkv_device_status": (_I, []),
+    "b200wkv_debug_split_plan": (_I, [_I, _I, _I, _P, _P]),
+    "b200wkv_debug_runs": (_I, [_I, _I, _I, _I, _P, _I]),
     "b200wkv7_residual_bytes": (_SZ, [_I, _I, _I, _I, _I]),
     "b200wkv7_fwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P, _P, _SZ, _U]),
     "b200wkv7_step_inplace": (_I, [_P, _I, _I, _I, _I] + [_P] * 6 + [_P, ctypes.c_longlong, _P, _P, _P]),

@@ -1,5 +1,6 @@
 // extern "C" entry points declared in include/b200wkv.h: argument validation and dispatch.
 #include "common.cuh"
+#include "chunk_common.cuh"
 
 namespace b200wkv {
 size_t wkv7_seq_residual_bytes(int B, int T, int H);
@@ -201,6 +202,28 @@ int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N, const vo
     if ((reinterpret_cast<uintptr_t>(state) & 15u) != 0 || (state_batch_stride * esz) % 16 != 0) return B200WKV_EUNSUPPORTED;
     return wkv7_step_stream((cudaStream_t)stream, dtype, B, H, w, r, k, v, a, b, state, length, new_starts, y, state,
                             state_batch_stride);
+}
+
+int b200wkv_debug_split_plan(int chains, int n_blk, int per_sm, int* grid, int* seg) {
+    if (chains < 1 || n_blk < 1 || per_sm < 1 || !grid || !seg) return B200WKV_ESHAPE;
+    const SplitPlan p = plan_split(chains, n_blk, per_sm);
+    *grid = p.grid;
+    *seg = p.seg;
+    return B200WKV_OK;
+}
+
+int b200wkv_debug_runs(int chains, int seg, int grid, int cta, int* runs, int capacity) {
+    if (chains < 1 || seg < 1 || grid < 1 || cta < 0 || cta >= grid || !runs) return B200WKV_ESHAPE;
+    const long long lo = (long long)chains * seg * cta / grid, hi = (long long)chains * seg * (cta + 1) / grid;
+    if (hi <= lo) return 0;
+    const int n = run_count(lo, hi, seg);
+    for (int order = 0; order < n && order < capacity; ++order) {
+        const RunPlan r = run_at(lo, hi, seg, order);
+        runs[3 * order] = r.chain;
+        runs[3 * order + 1] = r.seg_from;
+        runs[3 * order + 2] = r.seg_to;
+    }
+    return n;
 }
 
 static int check_shift(int dtype, int B, int T, int D, int M) {

@@ -81,8 +81,8 @@ struct RunPlan {
     int seg_from;   // first segment of the run, in walking order
     int seg_to;     // one past the last segment
 };
-__device__ __forceinline__ int run_count(long long lo, long long hi, int seg) { return (int)((hi - 1) / seg - lo / seg) + 1; }
-__device__ __forceinline__ RunPlan run_at(long long lo, long long hi, int seg, int order) {
+__host__ __device__ __forceinline__ int run_count(long long lo, long long hi, int seg) { return (int)((hi - 1) / seg - lo / seg) + 1; }
+__host__ __device__ __forceinline__ RunPlan run_at(long long lo, long long hi, int seg, int order) {
     const int first = (int)(lo / seg), n = run_count(lo, hi, seg);
     // walking order: the last run of the range, the middle runs, the first run of the range
     const int ri = (n == 1) ? 0 : (order == 0 ? n - 1 : (order == n - 1 ? 0 : order));
@@ -142,9 +142,14 @@ __device__ __forceinline__ void tile_mma_tf32(const float* A, int lda, const flo
 constexpr int TRI_SCR_PITCH = 36;
 constexpr int TRI_SCR_FLOATS = 32 * TRI_SCR_PITCH;
 
-template <int NT>
+struct NoHook {
+    __device__ __forceinline__ void operator()() const {}
+};
+// `before_last_barrier` runs in every thread just ahead of the final CTA barrier (a place to retire
+// asynchronous work that must be ordered before what the caller does next).
+template <int NT, typename Hook = NoHook>
 __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, float* __restrict__ X,
-                                               float* __restrict__ scr, int tid) {
+                                               float* __restrict__ scr, int tid, Hook before_last_barrier = Hook()) {
     // ---- diagonal blocks (threads 0..63) and zero fill of the blocks above the diagonal (the rest)
     if (tid < 64) {
         const int d = tid >> 4, c = tid & 15, o = d * 16;
@@ -202,22 +207,19 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
         tile_mma_tf32(X + (32 + m0) * LF_PITCH + 32, LF_PITCH, scr + n0, TRI_SCR_PITCH, X + (32 + m0) * LF_PITCH + n0,
                       LF_PITCH, 32, lane);
     }
+    before_last_barrier();
     __syncthreads();
 }
 
 // bf16 copy of a 64x64 fp32 matrix (pitch LF_PITCH) into rows 0..63 of an operand slab
-// `copy` (may be null): a second destination in global memory, laid out as a 64-row slab (column blocks of CB64)
 template <int NT>
-__device__ __forceinline__ void fp32_to_slab64(const float* __restrict__ X, unsigned char* slab, int cb, int tid,
-                                               unsigned char* copy = nullptr) {
+__device__ __forceinline__ void fp32_to_slab64(const float* __restrict__ X, unsigned char* slab, int cb, int tid) {
     for (int idx = tid; idx < 512; idx += NT) {
         const int row = idx & 63, blk = idx >> 6;
         float f[8];
         *reinterpret_cast<float4*>(&f[0]) = *reinterpret_cast<const float4*>(&X[row * LF_PITCH + blk * 8]);
         *reinterpret_cast<float4*>(&f[4]) = *reinterpret_cast<const float4*>(&X[row * LF_PITCH + blk * 8 + 4]);
-        const uint4 packed = pack8(f);
-        slab_store(slab, cb, row, blk, packed);
-        if (copy != nullptr) *reinterpret_cast<uint4*>(copy + blk * CB64 + row * 16) = packed;
+        slab_store(slab, cb, row, blk, pack8(f));
     }
 }
 

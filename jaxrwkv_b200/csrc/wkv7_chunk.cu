@@ -331,14 +331,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 for (int s = 0; s < 64; ++s) d[s] = (s < lim) ? d[s] : 0.f;
                 // A_ak -> M2A rows 0..63, P_rk -> M2A rows 64..127, P_rb -> TP rows 64..127
                 unsigned char* dst = smem + ((hsel == 1) ? OFF_M2A : OFF_TP);
-                unsigned char* kdst = keep == nullptr ? nullptr
-                                      : keep + (size_t)((row < 64) ? SAVED_AAK : (hsel == 1 ? SAVED_PRK : SAVED_PRB)) * SLAB64 + t * 16;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 packed = pack8(&d[c * 8]);
-                    slab_store(dst, CB128, row, c, packed);
-                    if (kdst != nullptr) *reinterpret_cast<uint4*>(kdst + c * CB64) = packed;
-                }
+                for (int c = 0; c < 8; ++c) slab_store(dst, CB128, row, c, pack8(&d[c * 8]));
             }
         }
         tc::fence_async_smem();
@@ -351,9 +345,19 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             mma_k64(tbase + D2, kmaj128(sM2A), mnmaj64(sV), ID_128x64_KM, true);
             tc::commit(&sm.bar[1]);
         }
+        // A_ak, P_rk and P_rb leave for the residual as bulk copies out of their slabs (one 64-row column
+        // block of 1 KB per lane of the last warp); the copies must have read M2A before G is written over it,
+        // which the hook in front of the inverse's last barrier guarantees
+        if (keep != nullptr && warp == 7 && lane < 24) {
+            const int which = lane >> 3, c = lane & 7;   // 0: A_ak, 1: P_rk, 2: P_rb
+            const unsigned char* src = smem + (which == 2 ? OFF_TP : OFF_M2A) + c * CB128 + (which == 0 ? 0 : 64 * 16);
+            unsigned char* dst = keep + (size_t)(which == 0 ? SAVED_AAK : (which == 1 ? SAVED_PRK : SAVED_PRB)) * SLAB64 + c * CB64;
+            tc::bulk_store(dst, src, 64 * 16);
+            tc::bulk_commit();
+        }
         PROF_MARK(8);
-        tri_inverse_64<256>(lf, xinv, scr, tid);
-        fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid, keep == nullptr ? nullptr : keep + (size_t)SAVED_T * SLAB64);
+        tri_inverse_64<256>(lf, xinv, scr, tid, [&]() { if (warp == 7) tc::bulk_wait_read<0>(); });
+        fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid);
         PROF_MARK(9);
         if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
@@ -368,6 +372,10 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_before_sync();
         __syncthreads();
         PROF_MARK(10);
+        if (keep != nullptr && warp == 7 && lane < 8) {   // T: rows 0..63 of the [Tinv ; P_rb] slab
+            tc::bulk_store(keep + (size_t)SAVED_T * SLAB64 + lane * CB64, smem + OFF_TP + lane * CB128, 64 * 16);
+            tc::bulk_commit();
+        }
         // ================= M3: sa = Tinv G =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -384,16 +392,16 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::tmem_ld32(lane_addr + D1 + hsel * 32, sa);
             tc::tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint4 packed = pack8(&sa[c * 8]);
-                slab_store(smem + OFF_SA, CB64, row, hsel * 4 + c, packed);
-                if (keep != nullptr) *reinterpret_cast<uint4*>(keep + (size_t)SAVED_SA * SLAB64 + (hsel * 4 + c) * CB64 + row * 16) = packed;
-            }
+            for (int c = 0; c < 4; ++c) slab_store(smem + OFF_SA, CB64, row, hsel * 4 + c, pack8(&sa[c * 8]));
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
         PROF_MARK(11);
+        if (keep != nullptr && tid == 7 * 32) {   // sa: the slab as it is (column-block padding included)
+            tc::bulk_store(keep + (size_t)SAVED_SA * SLAB64, smem + OFF_SA, SLAB64);
+            tc::bulk_commit();
+        }
         // ================= M4: Y += P_rb sa ; S += sa^T B^ + V^T K^ =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -419,9 +427,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         tc::fence_before_sync();
         PROF_MARK(13);
+        if (warp == 7) tc::bulk_wait_read<0>();   // the slabs copied out may be rewritten after the next barrier
         p = p1;
         par ^= 1u;
     }
+    if (warp == 7) tc::bulk_wait_all<0>();   // every copy to the residual has landed before the CTA retires
     if (failed) atomicExch(&g_status, 1);
     tc::fence_before_sync();
     __syncthreads();
