@@ -355,6 +355,38 @@ def test_chunk_bwd_sequences_split_across_ctas(T):
             assert rel_err(npf(a[bi]), npf(b[bi])) < TOL[torch.bfloat16], (n, bi, rel_err(npf(a[bi]), npf(b[bi])))
 
 
+def test_forward_backward_replay_from_a_cuda_graph():
+    """The calls only enqueue work (kernels, one small memset), so a forward + backward pair can be captured
+    into a CUDA graph and replayed on new data; shape chosen so that the backward runs in its split mode."""
+    B, T, H = 5, 256, 37
+    d = wkv7_case(B, T, H, seed=77, s0_scale=0.3, p_start=1 / 100, random_length=True)
+    t = to_dev(d, torch.bfloat16)
+    length, ns = (x.cuda() for x in flags(d))
+    length, ns = length.to(torch.int32), ns.to(torch.uint8)
+    gy = torch.randn_like(t["r"]); gs = torch.randn_like(t["s0"])
+    rwkv7.batched_wkv7_bwd(run_fwd(t, length, ns)[2], (gs, gy), B)     # first calls outside the capture
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            s, y, res = run_fwd(t, length, ns)
+            grads = rwkv7.batched_wkv7_bwd(res, (gs, gy), B)
+    torch.cuda.current_stream().wait_stream(side)
+    # new data in the captured input buffers, then replay
+    for n in NAMES7[:-1]:
+        t[n].copy_(torch.roll(t[n], 1, dims=0))
+    gy.copy_(torch.roll(gy, 1, dims=0))
+    graph.replay()
+    torch.cuda.synchronize()
+    s2, y2, res2 = run_fwd(t, length, ns)
+    grads2 = rwkv7.batched_wkv7_bwd(res2, (gs, gy), B)
+    assert torch.equal(y, y2) and torch.equal(s, s2)
+    for a, b in zip(grads, grads2):
+        assert torch.equal(a, b)
+
+
 def test_host_pipeline_matches_device_path():
     """wkv7_fwd_bwd_host (pinned host tensors in and out, batch sliced over three streams) returns
     exactly what the device-resident forward + backward return."""
