@@ -64,7 +64,7 @@ struct Small {
     float tot[kN];
     float lam[kN];
     float d_in[kN];        // D carried from the chunk processed before (later in time)
-    float d_part[4][kN];   // partial column sums of the new anchor (16 rows each)
+    float d_part[2][kN];   // partial column sums of the new anchor (32 rows each)
     float seg[4][kN];      // per-16-token totals of the decay-gradient scan
     uint64_t bar[7];       // 0..4 product rounds, 5 staging tiles, 6 operand slabs saved by the forward
     uint32_t nsm[2];       // chunk starts inside the current 64-token block
@@ -113,6 +113,11 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = warp & 3, hsel = warp >> 2;     // TMEM lane quadrant / column half handled by this warp
     const int row = quad * 32 + lane;                // TMEM lane == tile row
+    // Two threads issue the products of every round, each its own accumulators, so that issue (a serial
+    // instruction stream per thread) takes half as long; they sit in the warps with the least epilogue work.
+    // Both commit to the round's mbarrier (count 2).  The copy engines are driven from two other idle warps.
+    const bool issuer_a = (tid == 64), issuer_b = (tid == 192);
+    constexpr int kStageThread = 96, kSavedThread = 224;
     const size_t tok_stride = (size_t)H * kN;
     const int nBlk = (Tlen + kC - 1) / kC;
     // the sequence this CTA currently walks (set per run)
@@ -125,7 +130,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 7; ++i) tc::mbar_init(&sm.bar[i], 1);
+        for (int i = 0; i < 7; ++i) tc::mbar_init(&sm.bar[i], i < 5 ? 2 : 1);   // product rounds: one arrival per issuing thread
         tc::mbar_init_fence();
     }
     if (warp == 0) tc::tmem_alloc(&sm.tmem, 512);
@@ -202,7 +207,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     // 64 x 128 bytes per stream, all issued by one thread.  Rows past the chunk arrive too and are ignored.
     const int n_streams = (dy != nullptr) ? 7 : 6;
     auto issue_stage = [&](int cp) {
-        if (tid == 32) {   // not the thread that issues the products
+        if (tid == kStageThread) {
             tc::mbar_expect_tx(&sm.bar[5], (uint32_t)(n_streams * STG_TILE));
             const int x = (bh % H) * kN, y = bi * Tlen + cp;
 #pragma unroll
@@ -235,7 +240,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     // T|A_ak lie under staging tiles and follow once take_stage has emptied those.
     auto is_saved = [&](int cp, int cn) { return cn == kC && (cp & (kC - 1)) == 0; };
     auto issue_saved_late = [&](int cp) {
-        if (tid == 32) {
+        if (tid == kSavedThread) {
             const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
             tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(4 * SLAB64 + kC * kN * 2));
             tc::bulk_load(smem + OFF_PRB, src + SAVED_PRB * SLAB64, 2 * SLAB64, &sm.bar[6]);
@@ -246,7 +251,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
     };
     auto issue_saved_early = [&](int cp) {
-        if (tid == 32) {
+        if (tid == kSavedThread) {
             const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
             tc::bulk_load(smem + OFF_TINV, src + SAVED_T * SLAB64, 2 * SLAB64, &sm.bar[6]);
         }
@@ -417,9 +422,12 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 PROF_MARK(5);
             } else {
             // ================= R1: Gram blocks, A~ S0^T =================
-            if (tid == 0) {
+            if (issuer_a) {
                 tc::fence_after_sync();
                 mma_k64(tbase + T_D1, kmaj128(sAR), kmaj128(sBK), ID_N128_KK, false);
+                tc::commit(&sm.bar[0]);
+            } else if (issuer_b) {
+                tc::fence_after_sync();
                 mma_k64(tbase + T_G, kmaj128(sAR), kmaj64(sS0), ID_KK, false);
                 tc::commit(&sm.bar[0]);
             }
@@ -454,11 +462,14 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }   // recomputing chunk
             PROF_MARK(6);
             // ================= R2: G += A_ak V ; [Gd ; dVpart] = [B~;K~] dSL^T + [P_rb|P_rk]^T dY ; inverse =================
-            if (tid == 0) {
+            if (issuer_a) {
                 tc::fence_after_sync();
-                if (!cur_loaded) mma_k64(tbase + T_G, kmaj64(sAAK), mnmaj128(sVSA), ID_KM, true);
                 mma_k64(tbase + T_GD, kmaj128(sBK), kmaj64(sDSL), ID_KK, false);
                 mma_k64(tbase + T_GD, mnmaj64(sPRB), mnmaj128(sDD), ID_MM, true);
+                tc::commit(&sm.bar[1]);
+            } else if (issuer_b) {
+                tc::fence_after_sync();
+                if (!cur_loaded) mma_k64(tbase + T_G, kmaj64(sAAK), mnmaj128(sVSA), ID_KM, true);
                 tc::commit(&sm.bar[1]);
             }
             PROF_MARK(7);
@@ -489,10 +500,13 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             __syncthreads();
             PROF_MARK(9);
             // ================= R3: sa = T G ; dsa = T^T Gd =================
-            if (tid == 0) {
+            if (issuer_a) {
+                tc::fence_after_sync();
+                mma_k64(tbase + T_DSA, mnmaj64(sTINV), mnmaj64(sGD), ID_MM, false);
+                tc::commit(&sm.bar[2]);
+            } else if (issuer_b) {
                 tc::fence_after_sync();
                 if (!cur_loaded) mma_k64(tbase + T_SA, kmaj64(sTINV), mnmaj64(sG), ID_KM, false);
-                mma_k64(tbase + T_DSA, mnmaj64(sTINV), mnmaj64(sGD), ID_MM, false);
                 tc::commit(&sm.bar[2]);
             }
             if (quad < 2) {
@@ -517,10 +531,13 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             __syncthreads();
             PROF_MARK(10);
             // ================= R4: dV += A_ak^T dsa ; W = [V;sa][dY;dsa]^T ; tmp = dY^T R~ + dsa^T A~ =================
-            if (tid == 0) {
+            if (issuer_a) {
                 tc::fence_after_sync();
-                mma_k64(tbase + T_GD, mnmaj64(sTINV), mnmaj128(sDD + HALF), ID_MM, true);
                 mma_k64(tbase + T_D1, kmaj128(sVSA), kmaj128(sDD), ID_N128_KK, false);
+                mma_k64(tbase + T_GD, mnmaj64(sTINV), mnmaj128(sDD + HALF), ID_MM, true);
+                tc::commit(&sm.bar[3]);
+            } else if (issuer_b) {
+                tc::fence_after_sync();
                 mma_k64(tbase + T_TMP, mnmaj128(sDD), mnmaj128(sAR + HALF), ID_MM, false);
                 mma_k64(tbase + T_TMP, mnmaj128(sDD + HALF), mnmaj128(sAR), ID_MM, true);
                 tc::commit(&sm.bar[3]);
@@ -579,11 +596,14 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             __syncthreads();
             PROF_MARK(12);
             // ================= R5: [dK~';dB~'] and [dR~';dA~'] =================
-            if (tid == 0) {
+            if (issuer_a) {
                 tc::fence_after_sync();
                 mma_k64(tbase + T_KB, kmaj128(sWSA), mnmaj128(sAR), ID_KM, false);
                 mma_k64(tbase + T_KB, kmaj128(sWY), mnmaj128(sAR + HALF), ID_KM, true);
                 mma_k64(tbase + T_KB, kmaj128(sVSA), mnmaj64(sDSL), ID_KM, true);
+                tc::commit(&sm.bar[4]);
+            } else if (issuer_b) {
+                tc::fence_after_sync();
                 mma_k64(tbase + T_G, kmaj128(sDD), mnmaj64(sS0), ID_KM, false);
                 mma_k64(tbase + T_G, mnmaj128(sWY + HALF), mnmaj128(sBK), ID_MM, true);
                 mma_k64(tbase + T_G, mnmaj128(sWY), mnmaj128(sBK + HALF), ID_MM, true);
@@ -592,15 +612,15 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             // the rows of the next chunk (earlier in time) start travelling while the products run: their
             // tiles lie over buffers that the fourth round was the last to read
             if (has_next) issue_stage(p);
-            // exact anchor of the decay gradient for the chunk before: D = column sums of dS0 * S0 in fp32, by all
-            // threads (16 rows each) while the products run; the order of the additions is fixed
-            {
-                const int c = tid & 63, rq = tid >> 6;
+            // exact anchor of the decay gradient for the chunk before: D = column sums of dS0 * S0 in fp32 (32 rows
+            // per thread) while the products run; the order of the additions is fixed
+            if (quad < 2) {   // the warps that neither issue products nor drive a copy engine here
+                const int c = row, rq = hsel;
                 float acc = 0.f;
                 if (s0src != nullptr) {
 #pragma unroll 8
-                    for (int rr = 0; rr < 16; ++rr) {
-                        const int r0 = rq * 16 + rr;
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int r0 = rq * 32 + rr;
                         acc = fmaf(dsf[r0 * LF_PITCH + c], __ldg(s0src + r0 * kN + c), acc);
                     }
                 }
@@ -718,7 +738,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 __syncthreads();
                 // carry for the previous chunk: the exact anchor, or zero across a start flag
-                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : ((sm.d_part[0][tid] + sm.d_part[1][tid]) + (sm.d_part[2][tid] + sm.d_part[3][tid]));
+                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
                 __syncthreads();
                 if (row >= 64 && t < cur_n) {
                     float o[32];
