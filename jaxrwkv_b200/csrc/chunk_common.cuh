@@ -26,11 +26,12 @@ constexpr int kHandoffFloats = kN * kN + kN;
 inline size_t chunk_states_floats(int B, int T, int H) {
     return (size_t)B * H * ((size_t)((T + kC - 1) / kC) + 1) * kN * kN;
 }
-//   [B*H][ceil(T/64)][5 slabs]  for every 64-token block that the forward walked as ONE chunk: the bf16
-//                               operand slabs T = (I - A_ab)^-1, A_ak, P_rb, P_rk and sa exactly as the forward
-//                               used them, so the backward loads them instead of recomputing them
-constexpr int kSavedSlabs = 5;   // order: T, A_ak, P_rb, P_rk, sa (64-row slabs)
-constexpr int SAVED_T = 0, SAVED_AAK = 1, SAVED_PRB = 2, SAVED_PRK = 3, SAVED_SA = 4;
+//   [B*H][ceil(T/64)][6 slabs]  for every 64-token block that the forward walked as ONE chunk: the bf16
+//                               operand slabs T = (I - A_ab)^-1, A_ak, P_rb, P_rk, sa and the entering state S0
+//                               exactly as the forward used them, so the backward loads them instead of
+//                               recomputing them
+constexpr int kSavedSlabs = 6;   // order: T, A_ak, P_rb, P_rk, sa, S0 (64-row slabs)
+constexpr int SAVED_T = 0, SAVED_AAK = 1, SAVED_PRB = 2, SAVED_PRK = 3, SAVED_SA = 4, SAVED_S0 = 5;
 constexpr size_t kSavedBytes = (size_t)kSavedSlabs * SLAB64;
 inline size_t chunk_saved_offset_floats(int B, int T, int H) {
     return chunk_states_floats(B, T, H) + (size_t)kHandoffSlots * (kHandoffFloats + 1);

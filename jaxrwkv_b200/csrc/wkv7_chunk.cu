@@ -309,6 +309,10 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             mma_k64(tbase + D2, kmaj128(sAR), kmaj64(sS0), ID_128x64_KK, false);
             tc::commit(&sm.bar[0]);
         }
+        if (keep != nullptr && tid == 7 * 32) {   // the bf16 entering state goes to the residual as it is
+            tc::bulk_store(keep + (size_t)SAVED_S0 * SLAB64, smem + OFF_S0, SLAB64);
+            tc::bulk_commit();
+        }
         if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
         tc::fence_after_sync();
         PROF_MARK(6);
@@ -335,6 +339,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 for (int c = 0; c < 8; ++c) slab_store(dst, CB128, row, c, pack8(&d[c * 8]));
             }
         }
+        if (warp == 7) tc::bulk_wait_read<0>();   // the S0 slab has been read: the inverse writes over part of it next
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();

@@ -242,8 +242,9 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     auto issue_saved_late = [&](int cp) {
         if (tid == kSavedThread) {
             const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
-            tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(4 * SLAB64 + kC * kN * 2));
+            tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(5 * SLAB64 + kC * kN * 2));
             tc::bulk_load(smem + OFF_PRB, src + SAVED_PRB * SLAB64, 2 * SLAB64, &sm.bar[6]);
+            tc::bulk_load(smem + OFF_S0, src + SAVED_S0 * SLAB64, SLAB64, &sm.bar[6]);
             tc::bulk_prefetch_l2(src + SAVED_T * SLAB64, 2 * SLAB64);   // copied in later, from L2 then
 #pragma unroll
             for (int c = 0; c < 8; ++c)   // sa: rows 64..127 of the [V ; sa] slab, one column block at a time
@@ -393,21 +394,24 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             const float* s0src = reset_here ? nullptr : ((p % kC == 0) ? ckpt + ((size_t)bh * nBlk + p / kC) * kN * kN
                                                                         : s_at_len + st_base);
             {
-                float s[16], g[16];
-                if (s0src != nullptr) {
+                float g[16];
+                if (!cur_loaded) {   // (a loaded chunk gets the forward's own bf16 S0 slab by bulk copy)
+                    float s[16];
+                    if (s0src != nullptr) {
 #pragma unroll
-                    for (int c4 = 0; c4 < 4; ++c4) {
-                        const float4 x = *reinterpret_cast<const float4*>(s0src + si * kN + scq * 16 + c4 * 4);
-                        s[c4 * 4] = x.x; s[c4 * 4 + 1] = x.y; s[c4 * 4 + 2] = x.z; s[c4 * 4 + 3] = x.w;
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            const float4 x = *reinterpret_cast<const float4*>(s0src + si * kN + scq * 16 + c4 * 4);
+                            s[c4 * 4] = x.x; s[c4 * 4 + 1] = x.y; s[c4 * 4 + 2] = x.z; s[c4 * 4 + 3] = x.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) s[e] = 0.f;
                     }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) s[e] = 0.f;
+                    slab_store(smem + OFF_S0, CB64, si, scq * 2, pack8(s));
+                    slab_store(smem + OFF_S0, CB64, si, scq * 2 + 1, pack8(s + 8));
                 }
 #pragma unroll
                 for (int e = 0; e < 16; ++e) g[e] = dsf[si * LF_PITCH + scq * 16 + e] * sm.lam[scq * 16 + e];
-                slab_store(smem + OFF_S0, CB64, si, scq * 2, pack8(s));
-                slab_store(smem + OFF_S0, CB64, si, scq * 2 + 1, pack8(s + 8));
                 slab_store(smem + OFF_DSL, CB64, si, scq * 2, pack8(g));
                 slab_store(smem + OFF_DSL, CB64, si, scq * 2 + 1, pack8(g + 8));
             }
@@ -618,11 +622,11 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 const int c = row, rq = hsel;
                 float acc = 0.f;
                 if (s0src != nullptr) {
-#pragma unroll 8
-                    for (int rr = 0; rr < 32; ++rr) {
-                        const int r0 = rq * 32 + rr;
-                        acc = fmaf(dsf[r0 * LF_PITCH + c], __ldg(s0src + r0 * kN + c), acc);
-                    }
+                    float sv[32];   // all 32 loads in flight at once: their latency is paid once
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) sv[rr] = __ldg(s0src + (rq * 32 + rr) * kN + c);
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) acc = fmaf(dsf[(rq * 32 + rr) * LF_PITCH + c], sv[rr], acc);
                 }
                 sm.d_part[rq][c] = acc;
             }
