@@ -64,7 +64,7 @@ struct Small {
     float tot[kN];
     float lam[kN];
     float d_in[kN];        // D carried from the chunk processed before (later in time)
-    float d_part[2][kN];   // partial column sums of the new anchor (32 rows each)
+    float d_part[4][kN];   // partial column sums of the new anchor (16 rows each)
     float seg[4][kN];      // per-16-token totals of the decay-gradient scan
     uint64_t bar[7];       // 0..4 product rounds, 5 staging tiles, 6 operand slabs saved by the forward
     uint32_t nsm[2];       // chunk starts inside the current 64-token block
@@ -616,17 +616,17 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             // the rows of the next chunk (earlier in time) start travelling while the products run: their
             // tiles lie over buffers that the fourth round was the last to read
             if (has_next) issue_stage(p);
-            // exact anchor of the decay gradient for the chunk before: D = column sums of dS0 * S0 in fp32 (32 rows
+            // exact anchor of the decay gradient for the chunk before: D = column sums of dS0 * S0 in fp32 (16 rows
             // per thread) while the products run; the order of the additions is fixed
-            if (quad < 2) {   // the warps that neither issue products nor drive a copy engine here
-                const int c = row, rq = hsel;
+            {
+                const int c = tid & 63, rq = tid >> 6;
                 float acc = 0.f;
                 if (s0src != nullptr) {
-                    float sv[32];   // all 32 loads in flight at once: their latency is paid once
+                    float sv[16];   // all 16 loads in flight at once: their latency is paid once
 #pragma unroll
-                    for (int rr = 0; rr < 32; ++rr) sv[rr] = __ldg(s0src + (rq * 32 + rr) * kN + c);
+                    for (int rr = 0; rr < 16; ++rr) sv[rr] = __ldg(s0src + (rq * 16 + rr) * kN + c);
 #pragma unroll
-                    for (int rr = 0; rr < 32; ++rr) acc = fmaf(dsf[(rq * 32 + rr) * LF_PITCH + c], sv[rr], acc);
+                    for (int rr = 0; rr < 16; ++rr) acc = fmaf(dsf[(rq * 16 + rr) * LF_PITCH + c], sv[rr], acc);
                 }
                 sm.d_part[rq][c] = acc;
             }
@@ -742,7 +742,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 __syncthreads();
                 // carry for the previous chunk: the exact anchor, or zero across a start flag
-                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : (sm.d_part[0][tid] + sm.d_part[1][tid]);
+                if (tid < 64) sm.d_in[tid] = cur_reset ? 0.f : ((sm.d_part[0][tid] + sm.d_part[1][tid]) + (sm.d_part[2][tid] + sm.d_part[3][tid]));
                 __syncthreads();
                 if (row >= 64 && t < cur_n) {
                     float o[32];
