@@ -160,24 +160,16 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     while (true) {
         // ================= boundary at position p: TMEM holds the state after token p-1 =================
         const bool want_out = (p == L);
-        const bool want_ck = (ckpt != nullptr) && (p % kC == 0) && (p < Tlen);
-        if (quad < 2 && (want_out || want_ck)) {
+        if (quad < 2 && want_out) {
             float s[32];
             tc::tmem_ld32(lane_addr + DS + hsel * 32, s);
             tc::tmem_wait_ld();
-            if (want_out) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(s_out + st_row + c * 8) = pack8(&s[c * 8]);
-                if (s_at_len != nullptr) {
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(s_out + st_row + c * 8) = pack8(&s[c * 8]);
+            if (s_at_len != nullptr) {
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<float4*>(s_at_len + st_row + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
-                }
-            }
-            if (want_ck) {
-                float* dst = ckpt + (((size_t)bh * nBlk + p / kC) * kN + row) * kN + hsel * 32;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<float4*>(s_at_len + st_row + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
             }
         }
         if (p >= Tlen) break;
@@ -201,6 +193,16 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // a block walked as one full chunk leaves its operand slabs T, A_ak, P_rb, P_rk, sa for the backward
         unsigned char* const keep = (saved != nullptr && n == kC && (p & (kC - 1)) == 0)
                                         ? saved + ((size_t)bh * nBlk + (p >> 6)) * kSavedBytes : nullptr;
+        // the fp32 state entering a block is only needed by a backward that recomputes the block's first chunk,
+        // i.e. when that chunk is short; a full chunk passes its bf16 entering state with the saved slabs
+        if (quad < 2 && ckpt != nullptr && (p & (kC - 1)) == 0 && n < kC) {
+            float s[32];
+            tc::tmem_ld32(lane_addr + DS + hsel * 32, s);
+            tc::tmem_wait_ld();
+            float* dst = ckpt + (((size_t)bh * nBlk + p / kC) * kN + row) * kN + hsel * 32;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+        }
         PROF_MARK(1);
         // ================= stage inputs (registers), log-decay into the scan buffer =================
         uint4 raw[2][5];   // r, k, v, a, b

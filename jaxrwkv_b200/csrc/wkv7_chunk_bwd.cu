@@ -187,9 +187,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             const bool f = (pos < be) && (tid == 0 || flag || pos == L);
             const uint32_t m = __ballot_sync(0xffffffffu, f), mf = __ballot_sync(0xffffffffu, flag);
             if (lane == 0) { sm.nsm[warp] = m; sm.nsf[warp] = mf; }
-        } else if (b > 0 && tid < 64 + 128) {
-            // the saved state of the block processed after this one: one 128-byte line per thread towards L2
-            prefetch_l2(ckpt + ((size_t)bh * nBlk + b - 1) * kN * kN + (tid - 64) * 32);
         }
         fetch_flags(b - 1);
         __syncthreads();
@@ -621,7 +618,18 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             {
                 const int c = tid & 63, rq = tid >> 6;
                 float acc = 0.f;
-                if (s0src != nullptr) {
+                if (cur_loaded) {
+                    // a loaded chunk has no fp32 copy of its entering state: the bf16 slab the products use, read
+                    // from the residual (in L2 since the bulk copy) rather than from shared memory, whose bandwidth
+                    // the running products need for their operands
+                    const __nv_bfloat16* s0b = reinterpret_cast<const __nv_bfloat16*>(
+                                                   saved + ((size_t)bh * nBlk + (cur_p >> 6)) * kSavedBytes + SAVED_S0 * SLAB64 + (c >> 3) * CB64) + (c & 7);
+                    __nv_bfloat16 sv[16];   // all loads in flight at once
+#pragma unroll
+                    for (int rr = 0; rr < 16; ++rr) sv[rr] = __ldg(s0b + (rq * 16 + rr) * 8);
+#pragma unroll
+                    for (int rr = 0; rr < 16; ++rr) acc = fmaf(dsf[(rq * 16 + rr) * LF_PITCH + c], __bfloat162float(sv[rr]), acc);
+                } else if (s0src != nullptr) {
                     float sv[16];   // all 16 loads in flight at once: their latency is paid once
 #pragma unroll
                     for (int rr = 0; rr < 16; ++rr) sv[rr] = __ldg(s0src + (rq * 16 + rr) * kN + c);
