@@ -151,7 +151,10 @@ struct NoHook {
 template <int NT, typename Hook = NoHook>
 __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, float* __restrict__ X,
                                                float* __restrict__ scr, int tid, Hook before_last_barrier = Hook()) {
-    // ---- diagonal blocks (threads 0..63) and zero fill of the blocks above the diagonal (the rest)
+    // The 16- and 32-wide stages involve only the first four warps, which meet at a named barrier of their
+    // own; the other warps go straight to the CTA barrier in front of the 64-wide merge, so whatever they
+    // still have to do (issuing bulk copies, say) does not hold the first stages up.
+    // ---- diagonal blocks (threads 0..63) and zero fill of the blocks above the diagonal (threads 64..127)
     if (tid < 64) {
         const int d = tid >> 4, c = tid & 15, o = d * 16;
         float x[16];
@@ -172,8 +175,8 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
         }
 #pragma unroll
         for (int t = 0; t < 16; ++t) X[(o + t) * LF_PITCH + o + c] = x[t];
-    } else {
-        for (int idx = tid - 64; idx < 6 * 256; idx += NT - 64) {
+    } else if (tid < 128) {
+        for (int idx = tid - 64; idx < 6 * 256; idx += 64) {
             const int blk = idx >> 8, e = idx & 255;
             // blocks (bi, bj) with bj > bi: (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
             const int bi = (blk < 3) ? 0 : (blk < 5 ? 1 : 2);
@@ -181,19 +184,16 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
             X[(bi * 16 + (e >> 4)) * LF_PITCH + bj * 16 + (e & 15)] = 0.f;
         }
     }
-    __syncthreads();
     // ---- merges on the warp-level tensor path (m16n8k8, tf32 operands, fp32 accumulate): the result is
     // rounded to bf16 afterwards, so tf32's 11-bit mantissa costs nothing.  One 16x8 output tile per warp.
     const int warp = tid >> 5, lane = tid & 31;
     // 16 -> 32: W_q = L21 X11 for q = 0,1 (two 16x16 products = four tiles), then X21 = X22 W_q
     if (warp < 4) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         const int q = warp >> 1, n0 = (warp & 1) * 8, o = q * 32;
         tile_mma_tf32(L + (o + 16) * LF_PITCH + o, LF_PITCH, X + o * LF_PITCH + o + n0, LF_PITCH,
                       scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH, 16, lane);
-    }
-    __syncthreads();
-    if (warp < 4) {
-        const int q = warp >> 1, n0 = (warp & 1) * 8, o = q * 32;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         tile_mma_tf32(X + (o + 16) * LF_PITCH + o + 16, LF_PITCH, scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH,
                       X + (o + 16) * LF_PITCH + o + n0, LF_PITCH, 16, lane);
     }
