@@ -253,9 +253,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         PROF_MARK(3);
         // ================= scaled operands into the slabs =================
         {
-            float h1v[8], totv[8];
+            float h1v[8], lamv[8];   // first-half totals; 2^(chunk total) per channel
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { h1v[e] = sm.h1[jb * 8 + e]; totv[e] = sm.tot[jb * 8 + e]; }
+            for (int e = 0; e < 8; ++e) { h1v[e] = sm.h1[jb * 8 + e]; lamv[e] = sm.lam[jb * 8 + e]; }
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int t = q * 32 + tsub;
@@ -267,7 +267,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 for (int e = 0; e < 8; ++e) {
                     const float cc = fmaxf(c[e] + (q == 1 ? h1v[e] : 0.f), kCumFloor);
                     const float cp = fminf(fmaxf(cc - lw[q][e], kCumFloor), 0.f);   // cumulative log2-decay before this token
-                    eL[e] = ex2(cc); eI[e] = ex2(-cc); eP[e] = ex2(cp); eE[e] = ex2(totv[e] - cc);
+                    eL[e] = ex2(cc); eI[e] = ex2(-cc); eP[e] = ex2(cp);
+                    eE[e] = lamv[e] * eI[e];   // 2^(total - cc) without a fourth trip to the special-function unit
                 }
                 // raw: r, k, v, a, b
                 slab_store(smem + OFF_AR, CB128, t, jb, scale8(raw[q][3], eP));
