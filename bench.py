@@ -242,7 +242,7 @@ def main():
     achieved = dom_bytes / (dom_ms / 1e3) / 1e9
     # DRAM bytes per launch from the ncu capture at B=2 (summaries of both kernels are kept under profiles/:
     # dram__bytes_read.sum + dram__bytes_write.sum), scaled by B/2 because traffic is proportional to B
-    traffic = {"wkv7_bwd": 613.0e6, "wkv7_fwd": 397.7e6}[dom] * B / 2
+    traffic = {"wkv7_bwd": 612.4e6, "wkv7_fwd": 397.4e6}[dom] * B / 2
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": which,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                 "traffic_source": "ncu capture at B=2 scaled by B/2",
