@@ -1,6 +1,6 @@
 // RWKV-7 WKV forward, chunked along T on the Blackwell tensor cores (bf16 I/O, fp32 state).
 //
-// One CTA (128 threads) per (batch, head) walks the sequence in chunks of up to 64 tokens.  With
+// One CTA (256 threads) per (batch, head) walks the sequence in chunks of up to 64 tokens.  With
 // L_t = prod_{s<=t} decay_s (per key channel, inside the chunk) and the scaled operands
 //   A~_t = a_t * L_{t-1}   R~_t = r_t * L_t   B~_t = b_t / L_t   K~_t = k_t / L_t
 //   B^_t = b_t * L_C / L_t K^_t = k_t * L_C / L_t                (L_C = decay over the whole chunk)
@@ -16,6 +16,12 @@
 // stays in TMEM in fp32 for the whole sequence.  Start flags and `length` never need masks:
 // a chunk simply ends early in front of a start position and at `length`, and the rows of a
 // short chunk are zero-filled.
+//
+// Data movement: the raw rows of the next chunk arrive in shared memory by tiled bulk copies
+// (cp.async.bulk.tensor) while the current chunk finishes.  When a residual is requested, every block
+// walked as one full chunk leaves bf16 operand slabs for the backward (T, A_ak, P_rb, P_rk, sa, S0; most
+// of them by bulk stores out of shared memory) so that the backward need not recompute them; the fp32
+// state entering a block is written only when the block's first chunk is short.
 //
 // Semantics: BaseRWKV.inner_loop of jaxrwkv (src/jaxrwkv/rwkv7.py:199-220).
 #include "common.cuh"

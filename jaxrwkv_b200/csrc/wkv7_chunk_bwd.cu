@@ -1,8 +1,11 @@
 // RWKV-7 WKV backward, chunked along T on the Blackwell tensor cores (bf16 I/O, fp32 carries).
 //
-// One CTA (256 threads) per (batch, head) walks the chunks of the forward in reverse.  A chunk is
-// re-entered from the forward's saved state S0 and recomputed (scaled operands, the four
-// triangular Gram blocks, T = (I - A_ab)^-1, sa), then with dS = gradient of the state leaving
+// One persistent CTA (256 threads) per SM walks sequences, or runs of blocks of sequences, in reverse
+// (see RunPlan in chunk_common.cuh).  A chunk is re-entered from the forward's saved state S0; its
+// forward quantities (the four triangular Gram blocks, T = (I - A_ab)^-1, sa) are copied in from the
+// residual when the forward walked the block as one full chunk, and recomputed otherwise; the scaled
+// operands are always rebuilt from the raw rows, which arrive by tiled bulk copies one chunk ahead.
+// Then with dS = gradient of the state leaving
 // the chunk, L = in-chunk cumulative decay (L_C at the chunk end) and dSL = dS diag(L_C):
 //   dsa   = T^T (B~ dSL^T + P_rb^T dY)                           row t is dS_t b_t
 //   dV    = K~ dSL^T + P_rk^T dY + A_ak^T dsa
