@@ -19,16 +19,19 @@ struct DecaySrc {
 };
 
 // ------------------------------------------------------------------ forward ---------
-// 128 threads: warps 0-1 compute (thread v owns column v of S: the output is an in-thread dot product
-// over keys and every token-vector read is a warp-uniform broadcast); warps 2-3 stream the next chunk.
+// 192 threads: warps 0-3 compute, thread (v = tid % 64, half = tid / 64) owns keys 32 half .. 32 half + 31 of
+// column v of S: the output is an in-thread dot product over its keys (the two halves are added when the
+// chunk's outputs are flushed) and every token-vector read is a warp-uniform broadcast; warps 4-5 stream the
+// next chunk.  Half a column per thread halves the dependent instruction stream per token and the registers,
+// so that four CTAs fit on an SM.
 struct Fwd6Smem {
     float in[2][4][kCk6][kN];  // decay, r, k, v
-    float y[2][kCk6][kN];
+    float y[2][2][kCk6][kN];   // partial outputs of the two key halves
     uint8_t ns[2][kCk6];
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(192, 4)
 wkv6_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                     const T* __restrict__ w, int w_per_token, const T* __restrict__ u, const T* __restrict__ s0,
                     const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts, T* __restrict__ y,
@@ -37,8 +40,8 @@ wkv6_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restric
     Fwd6Smem& sm = *reinterpret_cast<Fwd6Smem*>(smem_raw);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x;
-    const bool streamer = tid >= 64;
-    const int i = tid & 63;
+    const bool streamer = tid >= 128;
+    const int i = tid & 63, half = (tid >> 6) & 1, k0 = half * 32;
     const size_t seq_base = (size_t)bi * Tlen * H * kN + (size_t)h * kN;
     const size_t tok_stride = (size_t)H * kN;
     const int L = min((int)length[bi], Tlen);
@@ -72,21 +75,24 @@ wkv6_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restric
 #pragma unroll
         for (int u4 = 0; u4 < 4; ++u4) {
             const int g = i + 64 * u4, lt = g >> 4, lc = (g & 15) * 4;
-            if (t0 + lt < Tlen)
-                store4(y + seq_base + (size_t)(t0 + lt) * tok_stride + lc, *reinterpret_cast<const float4*>(&sm.y[buf][lt][lc]));
+            if (t0 + lt < Tlen) {
+                const float4 a = *reinterpret_cast<const float4*>(&sm.y[buf][0][lt][lc]);
+                const float4 b = *reinterpret_cast<const float4*>(&sm.y[buf][1][lt][lc]);
+                store4(y + seq_base + (size_t)(t0 + lt) * tok_stride + lc, make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w));
+            }
         }
     };
 
-    float S[kN], uu[kN];
+    float S[32], uu[32];
     if (!streamer) {
 #pragma unroll
-        for (int kk = 0; kk < kN; ++kk) {
-            S[kk] = to_f32(s0[((size_t)bh * kN + kk) * kN + i]);
-            uu[kk] = to_f32(u[(size_t)h * kN + kk]);
+        for (int kk = 0; kk < 32; ++kk) {
+            S[kk] = to_f32(s0[((size_t)bh * kN + k0 + kk) * kN + i]);
+            uu[kk] = to_f32(u[(size_t)h * kN + k0 + kk]);
         }
         if (L == 0) {
 #pragma unroll
-            for (int kk = 0; kk < kN; ++kk) s_out[((size_t)bh * kN + kk) * kN + i] = from_f32<T>(S[kk]);
+            for (int kk = 0; kk < 32; ++kk) s_out[((size_t)bh * kN + k0 + kk) * kN + i] = from_f32<T>(S[kk]);
         }
     } else {
         stage(0, 0);
@@ -100,23 +106,23 @@ wkv6_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restric
             if (c + 1 < nC) stage(c + 1, buf ^ 1);
         } else {
             if (ckpt != nullptr) {
-                float* dst = ckpt + ((size_t)bh * nC + c) * kN * kN + i;
+                float* dst = ckpt + ((size_t)bh * nC + c) * kN * kN + (size_t)k0 * kN + i;
 #pragma unroll
-                for (int kk = 0; kk < kN; ++kk) dst[kk * kN] = S[kk];
+                for (int kk = 0; kk < 32; ++kk) dst[kk * kN] = S[kk];
             }
             const int nt = min(kCk6, Tlen - t0);
             for (int tt = 0; tt < nt; ++tt) {
                 if (sm.ns[buf][tt]) {
 #pragma unroll
-                    for (int kk = 0; kk < kN; ++kk) S[kk] = 0.f;
+                    for (int kk = 0; kk < 32; ++kk) S[kk] = 0.f;
                 }
                 const float vi = sm.in[buf][3][tt][i];
                 float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
 #pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    const float4 dv = *reinterpret_cast<const float4*>(&sm.in[buf][0][tt][g * 4]);
-                    const float4 rv = *reinterpret_cast<const float4*>(&sm.in[buf][1][tt][g * 4]);
-                    const float4 kv = *reinterpret_cast<const float4*>(&sm.in[buf][2][tt][g * 4]);
+                for (int g = 0; g < 8; ++g) {
+                    const float4 dv = *reinterpret_cast<const float4*>(&sm.in[buf][0][tt][k0 + g * 4]);
+                    const float4 rv = *reinterpret_cast<const float4*>(&sm.in[buf][1][tt][k0 + g * 4]);
+                    const float4 kv = *reinterpret_cast<const float4*>(&sm.in[buf][2][tt][k0 + g * 4]);
                     float* s4 = &S[g * 4];
                     const float* u4 = &uu[g * 4];
                     const float a0 = kv.x * vi, a1 = kv.y * vi, a2 = kv.z * vi, a3 = kv.w * vi;
@@ -125,10 +131,10 @@ wkv6_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restric
                     s4[0] = fmaf(dv.x, s4[0], a0); s4[1] = fmaf(dv.y, s4[1], a1);
                     s4[2] = fmaf(dv.z, s4[2], a2); s4[3] = fmaf(dv.w, s4[3], a3);
                 }
-                sm.y[buf][tt][i] = (y0 + y1) + (y2 + y3);
+                sm.y[buf][half][tt][i] = (y0 + y1) + (y2 + y3);
                 if (t0 + tt == L - 1) {
 #pragma unroll
-                    for (int kk = 0; kk < kN; ++kk) s_out[((size_t)bh * kN + kk) * kN + i] = from_f32<T>(S[kk]);
+                    for (int kk = 0; kk < 32; ++kk) s_out[((size_t)bh * kN + k0 + kk) * kN + i] = from_f32<T>(S[kk]);
                 }
             }
         }
@@ -372,7 +378,7 @@ int launch_fwd6(cudaStream_t st, int B, int Tlen, int H, const void* r, const vo
     auto kern = wkv6_seq_fwd_kernel<T>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Fwd6Smem)) != cudaSuccess)
         return B200WKV_ELAUNCH;
-    kern<<<B * H, 128, sizeof(Fwd6Smem), st>>>(Tlen, H, (const T*)r, (const T*)k, (const T*)v, (const T*)w, per_token,
+    kern<<<B * H, 192, sizeof(Fwd6Smem), st>>>(Tlen, H, (const T*)r, (const T*)k, (const T*)v, (const T*)w, per_token,
                                                (const T*)u, (const T*)s0, length, ns, (T*)y, (T*)s_out, (float*)residual);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
