@@ -159,7 +159,7 @@ struct Bwd6Smem {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 wkv6_seq_bwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                     const T* __restrict__ w, int w_per_token, const T* __restrict__ u,
                     const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
