@@ -39,6 +39,7 @@ extern "C" {
 #define B200WKV_ELAUNCH      -5   /* the CUDA runtime refused the launch                 */
 #define B200WKV_EUNSUPPORTED -6   /* combination not available in this build             */
 #define B200WKV_ESCRATCH     -7   /* problem larger than a fixed built-in scratch area   */
+#define B200WKV_ESYMBOL      -8   /* the built-in scratch area could not be materialised  */
 
 /* flags (bit set) */
 #define B200WKV_FLAG_SEQUENTIAL 1u   /* force the token-sequential CUDA-core kernels     */
@@ -51,14 +52,6 @@ int b200wkv_abi_version(void);
  * recorded there (1 = forward, 2 = backward) and the kernel still terminates.  This call
  * synchronises the device, so it is not for the hot path.  Returns -1 if the CUDA runtime fails. */
 int b200wkv_device_status(void);
-
-/* Diagnostics of the work split used by the tensor-core backward (no GPU needed; for tests).
- * split_plan: grid size and segments per sequence chosen for `chains` = B*H sequences of `n_blk`
- * 64-token blocks with `per_sm` resident thread blocks per SM.  runs: the pieces thread block `cta` of
- * `grid` walks, in walking order, as (sequence, first segment, one-past-last segment) triples written to
- * `runs` (at most `capacity` of them); returns their number. */
-int b200wkv_debug_split_plan(int chains, int n_blk, int per_sm, int* grid, int* seg);
-int b200wkv_debug_runs(int chains, int seg, int grid, int cta, int* runs, int capacity);
 
 /* ---------------------------------------------------------------- RWKV-7 ----
  * Replaces the XLA custom calls "wkv7-fwd-{fp32,bf16}" / "wkv7-bwd-{fp32,bf16}"
@@ -114,7 +107,7 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N,
                  const void* a, const void* b, const void* s0,
                  const uint32_t* length, const uint8_t* new_starts,
                  const void* dy, const void* ds_out,
-                 const void* residual, size_t residual_bytes,
+                 void* residual, size_t residual_bytes,
                  void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
                  unsigned flags);
 
@@ -196,7 +189,11 @@ int b200wkv_token_shift_bwd(void* stream, int dtype, int B, int T, int D, int M,
  * the process exits).  Problems whose b200wkv7_residual_bytes() exceeds that size are refused
  * with B200WKV_ESCRATCH and nothing is launched.  The call itself never calls cudaMalloc/cudaFree
  * or any allocating routine; the first call on each device resolves the array's device address
- * (make that first call before starting a stream capture on that device).  All calls on a device
+ * (make that first call before starting a stream capture on that device).  Because CUDA loads
+ * modules lazily by default, that first call is also where the driver materialises the array on the
+ * device: it can take device memory and synchronise, and it returns B200WKV_ESYMBOL if none is left -
+ * so make it (or set CUDA_MODULE_LOADING=EAGER) before a framework's memory pool claims the device.
+ * Every argument is checked before anything is enqueued.  All calls on a device
  * share the one array and it keeps the previous call's contents (nothing in it needs clearing: the
  * forward rewrites every slot the backward reads), so two calls must not overlap on the GPU -
  * issue them on one stream or order them with events.

@@ -48,8 +48,13 @@ def batched_wkv6_bwd(version, res, grads, B):
     lib = _lib.load()
     r, k, v, w, u, s, length, new_starts, residual = res
     gs_out, gy = grads
+    # dense C-order buffers for the kernel (see batched_wkv7_bwd): views and broadcasts are materialised
+    r, k, v, w, u, s = (x.contiguous() for x in (r, k, v, w, u, s))
+    length = length.to(device=k.device, dtype=torch.int32).contiguous()
+    new_starts = new_starts.to(device=k.device, dtype=torch.uint8).contiguous()
     code = _lib.dtype_code(k.dtype)
     _, T, H, N = k.shape
+    assert length.shape == (B,) and new_starts.shape == (B, T)
     gy = None if gy is None else gy.to(k.dtype).contiguous()
     gs_out = None if gs_out is None else gs_out.to(k.dtype).contiguous()
     gr, gk, gv = (torch.empty_like(k) for _ in range(3))

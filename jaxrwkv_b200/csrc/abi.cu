@@ -1,16 +1,18 @@
 // extern "C" entry points declared in include/b200wkv.h: argument validation and dispatch.
 #include "common.cuh"
 #include "chunk_common.cuh"
+#include "../../include/b200wkv_debug.h"
 
 namespace b200wkv {
 size_t wkv7_seq_residual_bytes(int B, int T, int H);
 int wkv7_seq_fwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w, const void* r, const void* k,
                  const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
-                 const uint8_t* ns, void* y, void* s_out, void* residual);
+                 const uint8_t* ns, void* y, void* s_out, void* residual, const int* run_if, int run_ticket,
+                 int* residual_mark);
 int wkv7_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w, const void* r, const void* k,
                  const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
                  const uint8_t* ns, const void* dy, const void* ds_out, const void* residual, void* dw, void* dr,
-                 void* dk, void* dv, void* da, void* db, void* ds0);
+                 void* dk, void* dv, void* da, void* db, void* ds0, const int* run_if);
 
 int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
               const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
@@ -21,11 +23,11 @@ int wkv7_step_stream(cudaStream_t st, int dtype, int B, int H, const void* w, co
 size_t wkv7_chunk_residual_bytes(int B, int T, int H);
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
-                   void* s_out, void* residual, void* dbg);
+                   void* s_out, void* residual, int* residual_mark, int** range_flag, int* range_ticket);
 int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
-                   const void* ds_out, const void* residual, void* dw, void* dr, void* dk, void* dv, void* da,
-                   void* db, void* ds0);
+                   const void* ds_out, void* residual, const int* residual_mark, void* dw, void* dr, void* dk, void* dv,
+                   void* da, void* db, void* ds0);
 int wkv7_chunk_status();
 
 size_t wkv6_seq_residual_bytes(int B, int T, int H);
@@ -48,6 +50,14 @@ int token_shift_fwd(cudaStream_t st, int dtype, int B, int T, int D, int M, cons
 int token_shift_bwd(cudaStream_t st, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
                     const void* mix, const uint32_t* length, const uint8_t* ns, const void* gout, const void* gstate,
                     void* gx, void* gprev, void* gmix);
+
+// The bf16 forward normally runs the chunked tensor-core kernel; a decay outside that kernel's range makes
+// the token-sequential kernel behind it redo the call.  The last bytes of the residual tell the backward
+// which of the two wrote it.
+constexpr size_t kResidualMarkBytes = 16;
+static int* residual_mark_of(void* residual, size_t bytes) {
+    return residual ? reinterpret_cast<int*>(static_cast<char*>(residual) + bytes - kResidualMarkBytes) : nullptr;
+}
 
 static int check_dims(int dtype, int B, int T, int H, int N) {
     if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
@@ -72,11 +82,12 @@ const char* b200wkv_strerror(int status) {
         case B200WKV_ELAUNCH: return "CUDA kernel launch failed";
         case B200WKV_EUNSUPPORTED: return "combination not available in this build";
         case B200WKV_ESCRATCH: return "problem exceeds the fixed built-in scratch area";
+        case B200WKV_ESYMBOL: return "the built-in scratch area could not be materialised on this device (module load failed: out of device memory?)";
         default: return "unknown status";
     }
 }
 
-int b200wkv_abi_version(void) { return 1; }
+int b200wkv_abi_version(void) { return 2; }
 
 int b200wkv_device_status(void) { return wkv7_chunk_status(); }
 
@@ -87,7 +98,8 @@ size_t b200wkv7_residual_bytes(int dtype, int B, int T, int H, int N) {
     const size_t seq = wkv7_seq_residual_bytes(B, T, H);
     if (dtype == B200WKV_F32) return seq;
     const size_t chk = wkv7_chunk_residual_bytes(B, T, H);
-    return seq > chk ? seq : chk;
+    // + one word at the end that says which of the two formats the forward left (see residual_mark_of)
+    return (seq > chk ? seq : chk) + kResidualMarkBytes;
 }
 
 int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void* w, const void* r, const void* k,
@@ -101,16 +113,23 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void
     // one token and no residual wanted (recurrent decoding): a single pass over the state
     if (T == 1 && residual == nullptr)
         return wkv7_step((cudaStream_t)stream, dtype, B, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out);
-    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL))
-        return wkv7_chunk_fwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
-                              residual, nullptr);
+    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL)) {
+        int* mark = residual_mark_of(residual, b200wkv7_residual_bytes(dtype, B, T, H, N));
+        int *range_flag = nullptr, ticket = 0;
+        st = wkv7_chunk_fwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out, residual, mark,
+                            &range_flag, &ticket);
+        if (st != B200WKV_OK) return st;
+        // does nothing unless the kernel above met a decay outside its range and left its ticket
+        return wkv7_seq_fwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out, residual,
+                            range_flag, ticket, mark);
+    }
     return wkv7_seq_fwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, y, s_out,
-                        residual);
+                        residual, nullptr, 0, nullptr);
 }
 
 int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void* w, const void* r, const void* k,
                  const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
-                 const uint8_t* new_starts, const void* dy, const void* ds_out, const void* residual,
+                 const uint8_t* new_starts, const void* dy, const void* ds_out, void* residual,
                  size_t residual_bytes, void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
                  unsigned flags) {
     int st = check_dims(dtype, B, T, H, N);
@@ -120,11 +139,16 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void
         return B200WKV_ENULL;
     if (residual_bytes < b200wkv7_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
     // must match the kernel family that filled the residual in b200wkv7_fwd (same dtype and flags)
-    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL))
-        return wkv7_chunk_bwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, length, new_starts, dy, ds_out,
-                              residual, dw, dr, dk, dv, da, db, ds0);
+    if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL)) {
+        const int* mark = residual_mark_of(residual, b200wkv7_residual_bytes(dtype, B, T, H, N));
+        st = wkv7_chunk_bwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, length, new_starts, dy, ds_out, residual, mark,
+                            dw, dr, dk, dv, da, db, ds0);
+        if (st != B200WKV_OK) return st;
+        return wkv7_seq_bwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, dy, ds_out,
+                            residual, dw, dr, dk, dv, da, db, ds0, mark);
+    }
     return wkv7_seq_bwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, dy, ds_out,
-                        residual, dw, dr, dk, dv, da, db, ds0);
+                        residual, dw, dr, dk, dv, da, db, ds0, nullptr);
 }
 
 size_t b200wkv6_residual_bytes(int dtype, int B, int T, int H, int N) {
@@ -206,7 +230,7 @@ int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N, const vo
 
 int b200wkv_debug_split_plan(int chains, int n_blk, int per_sm, int* grid, int* seg) {
     if (chains < 1 || n_blk < 1 || per_sm < 1 || !grid || !seg) return B200WKV_ESHAPE;
-    const SplitPlan p = plan_split(chains, n_blk, per_sm);
+    const SplitPlan p = plan_split(chains, n_blk, per_sm, sm_count_of_current_device());
     *grid = p.grid;
     *seg = p.seg;
     return B200WKV_OK;

@@ -1,6 +1,7 @@
 // Constants and small helpers shared by the chunked (tcgen05) forward and backward kernels.
 #pragma once
 #include "common.cuh"
+#include "device_once.cuh"
 
 namespace b200wkv {
 
@@ -41,19 +42,13 @@ inline size_t chunk_residual_floats(int B, int T, int H) {
 }
 
 // Host side of the split: grid size and segments per sequence for `chains` sequences of `n_blk`
-// blocks with `per_sm` resident CTAs per SM.
+// blocks with `per_sm` resident CTAs per SM on a device of `sm_count` SMs (the launchers pass the
+// count of the device that is current, looked up once per device).
 struct SplitPlan {
     int grid;
     int seg;
 };
-inline SplitPlan plan_split(int chains, int n_blk, int per_sm) {
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-            sm_count = 148;
-    }
+inline SplitPlan plan_split(int chains, int n_blk, int per_sm, int sm_count) {
     const int slots = sm_count * per_sm;
     SplitPlan p{chains, 1};
     if (chains <= slots) return p;            // every sequence gets its own resident CTA

@@ -4,6 +4,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
+
+#include <mutex>
 
 namespace b200wkv {
 
@@ -12,16 +15,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn tmap_encoder() {
+    static std::once_flag once;
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    std::call_once(once, []() {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
+    });
     return fn;
 }
 
@@ -45,9 +47,33 @@ inline bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows,
 struct StreamMaps {
     CUtensorMap m[7];
 };
+
+// A tensor map depends only on (base address, shape), and a training loop calls with the same buffers
+// step after step, so each host thread remembers the last few sets it encoded (thread-local: no lock,
+// nothing shared between the executor threads of different devices).
+struct StreamMapKey {
+    const void* base[7];
+    int count, B, T, H;
+};
 inline bool make_stream_maps(StreamMaps* out, const void* const* bases, int count, int B, int T, int H) {
+    constexpr int kSlots = 8;
+    struct Slot { StreamMapKey key; StreamMaps maps; bool used; };
+    thread_local Slot cache[kSlots];
+    thread_local int next = 0;
+    StreamMapKey key;
+    memset(&key, 0, sizeof(key));
+    for (int m = 0; m < 7; ++m) key.base[m] = bases[m < count ? m : 0];
+    key.count = count; key.B = B; key.T = T; key.H = H;
+    for (int i = 0; i < kSlots; ++i)
+        if (cache[i].used && memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
+            *out = cache[i].maps;
+            return true;
+        }
     for (int m = 0; m < 7; ++m)
-        if (!make_tmap_bf16_2d(&out->m[m], bases[m < count ? m : 0], (uint64_t)B * T, (uint64_t)H * 64, 64, 64)) return false;
+        if (!make_tmap_bf16_2d(&out->m[m], key.base[m], (uint64_t)B * T, (uint64_t)H * 64, 64, 64)) return false;
+    Slot& s = cache[next];
+    next = (next + 1) % kSlots;
+    s.key = key; s.maps = *out; s.used = true;
     return true;
 }
 

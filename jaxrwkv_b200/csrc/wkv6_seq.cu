@@ -7,6 +7,7 @@
 // (RWKV-5 / 5.2).  Semantics: BaseRWKV.inner_loop of jaxrwkv, src/jaxrwkv/rwkv6.py:174-191,
 // rwkv5_2.py:164-180, rwkv5.py:161-177; the backward is the reverse-time recurrence of that loop.
 #include "common.cuh"
+#include "device_once.cuh"
 
 namespace b200wkv {
 
@@ -376,7 +377,8 @@ int launch_fwd6(cudaStream_t st, int B, int Tlen, int H, const void* r, const vo
                 int per_token, const void* u, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
                 void* s_out, void* residual) {
     auto kern = wkv6_seq_fwd_kernel<T>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Fwd6Smem)) != cudaSuccess)
+    static DeviceOnce smem_attr;   // one per template instance; the attribute is per device
+    if (!smem_attr.ok([kern]() { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Fwd6Smem)); }))
         return B200WKV_ELAUNCH;
     kern<<<B * H, 192, sizeof(Fwd6Smem), st>>>(Tlen, H, (const T*)r, (const T*)k, (const T*)v, (const T*)w, per_token,
                                                (const T*)u, (const T*)s0, length, ns, (T*)y, (T*)s_out, (float*)residual);
@@ -388,7 +390,8 @@ int launch_bwd6(cudaStream_t st, int B, int Tlen, int H, const void* r, const vo
                 int per_token, const void* u, const uint32_t* length, const uint8_t* ns, const void* dy,
                 const void* ds_out, const void* residual, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0) {
     auto kern = wkv6_seq_bwd_kernel<T>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd6Smem)) != cudaSuccess)
+    static DeviceOnce smem_attr;   // one per template instance; the attribute is per device
+    if (!smem_attr.ok([kern]() { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd6Smem)); }))
         return B200WKV_ELAUNCH;
     kern<<<B * H, 256, sizeof(Bwd6Smem), st>>>(Tlen, H, (const T*)r, (const T*)k, (const T*)v, (const T*)w, per_token,
                                                (const T*)u, length, ns, (const T*)dy, (const T*)ds_out,

@@ -29,6 +29,8 @@
 #include "chunk_common.cuh"
 #include "tmap.cuh"
 
+#include <atomic>
+
 namespace b200wkv {
 
 namespace {
@@ -74,12 +76,6 @@ __device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, 
 
 __device__ int g_status;  // last device-side error (0 = none); see wkv7_chunk_status()
 
-#ifdef WKV_PROF
-__device__ long long g_prof[16];   // cycles per phase, summed over the chunks of CTA 0 (profiling builds only)
-#define PROF_MARK(i) do { if (bh == 0 && tid == 0) { const long long now_ = clock64(); g_prof[i] += now_ - prof_t_; prof_t_ = now_; } } while (0)
-#else
-#define PROF_MARK(i) do { } while (0)
-#endif
 
 // 256 threads: warp = (quad, hsel); quad selects the 32 TMEM lanes (tile rows) the warp may access,
 // hsel the column half it works on, so every accumulator tile is shared by two warps per row group.
@@ -90,7 +86,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
                       __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
-                      const __grid_constant__ StreamMaps maps, unsigned char* __restrict__ saved) {
+                      const __grid_constant__ StreamMaps maps, unsigned char* __restrict__ saved,
+                      int* __restrict__ range_flag, int range_ticket, int* __restrict__ residual_mark) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -107,6 +104,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
         for (int i = 0; i < 5; ++i) tc::mbar_init(&sm.bar[i], 1);
         tc::mbar_init_fence();
+        if (bh == 0 && residual_mark != nullptr) *residual_mark = 0;   // this residual is in the chunked format (so far)
     }
     if (warp == 0) tc::tmem_alloc(&sm.tmem, 256);
     tc::fence_before_sync();
@@ -160,9 +158,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
     };
     issue_stage(0);
-#ifdef WKV_PROF
-    long long prof_t_ = clock64();
-#endif
     while (true) {
         // ================= boundary at position p: TMEM holds the state after token p-1 =================
         const bool want_out = (p == L);
@@ -179,8 +174,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
         if (p >= Tlen) break;
-
-        PROF_MARK(0);
         // ================= extent of this chunk =================
         const int be = min(((p >> 6) + 1) << 6, Tlen);
         if (tid < 64) {
@@ -209,7 +202,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
             for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(dst + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
         }
-        PROF_MARK(1);
         // ================= stage inputs (registers), log-decay into the scan buffer =================
         uint4 raw[2][5];   // r, k, v, a, b
         float lw[2][8];    // log2 of the decay: -exp(w) * log2(e)
@@ -236,7 +228,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
         }
         __syncthreads();
-        PROF_MARK(2);
         if (tid < 128) {   // inclusive scan over tokens, two independent halves of 32 per channel
             const int j = tid & 63, half = tid >> 6;
             float run = 0.f;
@@ -251,12 +242,16 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         __syncthreads();
         if (tid < 64) {
-            const float t2 = fmaxf(sm.h1[tid] + sm.tot[tid], kCumFloor);
+            const float total = sm.h1[tid] + sm.tot[tid];
+            // A decay so strong that 1 / L leaves the range the products can carry (never reached by decays
+            // of the model's own parametrisation): the chunked form cannot represent this chunk.  Record it;
+            // the token-sequential kernel launched behind this one redoes the call when it finds the mark.
+            if (total < kCumFloor) atomicExch(range_flag, range_ticket);
+            const float t2 = fmaxf(total, kCumFloor);
             sm.tot[tid] = t2;
             sm.lam[tid] = ex2(t2);
         }
         __syncthreads();
-        PROF_MARK(3);
         // ================= scaled operands into the slabs =================
         {
             float h1v[8], lamv[8];   // first-half totals; 2^(chunk total) per channel
@@ -286,7 +281,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 slab_store(smem + OFF_V, CB64, t, jb, raw[q][2]);
             }
         }
-        PROF_MARK(4);
         // ================= entering state: bf16 copy for the products, decayed fp32 copy back to TMEM =====
         if (quad < 2) {
             float s[32];
@@ -310,7 +304,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
-        PROF_MARK(5);
         // ================= M1: pairwise products and the S0 products =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -324,7 +317,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
         tc::fence_after_sync();
-        PROF_MARK(6);
         // ================= E1: triangular masks, operands of the next products =================
         {
             const int t = row & 63;
@@ -352,7 +344,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
-        PROF_MARK(7);
         // ================= M2: G += A_ak V, Ypart += P_rk V ; meanwhile the triangular inverse =================
         if (tid == 0) {
             tc::fence_after_sync();
@@ -369,10 +360,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::bulk_store(dst, src, 64 * 16);
             tc::bulk_commit();
         }
-        PROF_MARK(8);
         tri_inverse_64<256>(lf, xinv, scr, tid, [&]() { if (warp == 7) tc::bulk_wait_read<0>(); });
         fp32_to_slab64<256>(xinv, smem + OFF_TP, CB128, tid);
-        PROF_MARK(9);
         if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
             tc::fence_after_sync();
@@ -385,7 +374,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
-        PROF_MARK(10);
         if (keep != nullptr && warp == 7 && lane < 8) {   // T: rows 0..63 of the [Tinv ; P_rb] slab
             tc::bulk_store(keep + (size_t)SAVED_T * SLAB64 + lane * CB64, smem + OFF_TP + lane * CB128, 64 * 16);
             tc::bulk_commit();
@@ -411,7 +399,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
-        PROF_MARK(11);
         if (keep != nullptr && tid == 7 * 32) {   // sa: the slab as it is (column-block padding included)
             tc::bulk_store(keep + (size_t)SAVED_SA * SLAB64, smem + OFF_SA, SLAB64);
             tc::bulk_commit();
@@ -427,7 +414,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if (tid < 64) flag_ahead = (p1 + tid < Tlen) ? new_starts[(size_t)bi * Tlen + p1 + tid] : 0;   // next chunk's start flags
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
-        PROF_MARK(12);
         if (quad >= 2) {
             const int t = row - 64;
             float yv[32];
@@ -440,7 +426,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             }
         }
         tc::fence_before_sync();
-        PROF_MARK(13);
         if (warp == 7) tc::bulk_wait_read<0>();   // the slabs copied out may be rewritten after the next barrier
         p = p1;
         par ^= 1u;
@@ -456,12 +441,39 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
 size_t wkv7_chunk_residual_bytes(int B, int T, int H) { return chunk_residual_floats(B, T, H) * sizeof(float); }
 
+// A forward call that meets a decay outside the chunked kernels' range tells the fallback launched behind
+// it through one int of device memory.  Calls may be in flight on several streams, so each call takes the
+// next slot of a small ring and a ticket that no earlier call used: a slot never needs clearing.
+__device__ int g_range_flags[64];
+
+static int* range_flag_ring() {
+    static DeviceOnce once;
+    static int* addr[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0) return nullptr;
+    if (!once.ok([dev]() {
+            int* ptr = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_range_flags);
+            addr[dev] = (e == cudaSuccess) ? ptr : nullptr;
+            return e;
+        }))
+        return nullptr;
+    return addr[dev];
+}
+
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
-                   void* s_out, void* residual, void* dbg) {
+                   void* s_out, void* residual, int* residual_mark, int** range_flag, int* range_ticket) {
     typedef __nv_bfloat16 bf;
-    if (cudaFuncSetAttribute(wkv7_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    static DeviceOnce smem_attr;   // the opt-in to large dynamic shared memory is a per-device function attribute
+    if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv7_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); }))
         return B200WKV_ELAUNCH;
+    static std::atomic<unsigned> tickets{1};
+    int* ring = range_flag_ring();
+    if (ring == nullptr) return B200WKV_ELAUNCH;
+    const unsigned ticket = tickets.fetch_add(1);
+    *range_flag = ring + (ticket & 63u);
+    *range_ticket = (int)(ticket | 0x40000000u);   // never 0, so untouched memory cannot match
     StreamMaps maps;
     const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]
     if (!make_stream_maps(&maps, bases, 6, B, T, H)) return B200WKV_ELAUNCH;
@@ -470,25 +482,26 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                                                           (bf*)y, (bf*)s_out, (float*)residual,
                                                           residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
                                                           maps,
-                                                          residual ? (unsigned char*)((float*)residual + chunk_saved_offset_floats(B, T, H)) : nullptr);
-    (void)dbg;
+                                                          residual ? (unsigned char*)((float*)residual + chunk_saved_offset_floats(B, T, H)) : nullptr,
+                                                          *range_flag, *range_ticket, residual_mark);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
+// Device address of the status word on the current device (resolved once per device).
 int* wkv7_chunk_status_word() {
-    int* ptr = nullptr;
-    if (cudaGetSymbolAddress((void**)&ptr, g_status) != cudaSuccess) return nullptr;
-    return ptr;
+    static DeviceOnce once;
+    static int* addr[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0) return nullptr;
+    if (!once.ok([dev]() {
+            int* ptr = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_status);
+            addr[dev] = (e == cudaSuccess) ? ptr : nullptr;
+            return e;
+        }))
+        return nullptr;
+    return addr[dev];
 }
-
-#ifdef WKV_PROF
-extern "C" int b200wkv_debug_prof(long long* out, int clear) {
-    long long zero[16] = {};
-    if (cudaMemcpyFromSymbol(out, g_prof, sizeof(zero)) != cudaSuccess) return -1;
-    if (clear) cudaMemcpyToSymbol(g_prof, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 // Reads and clears the device-side error word (synchronises the device; diagnostics only).
 int wkv7_chunk_status() {

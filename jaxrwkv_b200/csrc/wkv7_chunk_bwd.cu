@@ -86,12 +86,6 @@ constexpr uint32_t T_DSA = 320;   // 64 : dsa
 constexpr uint32_t T_TMP = 384;   // 64 : dsa^T A~ + dY^T R~
 constexpr uint32_t T_KB = 448;    // 64 : [dK~' ; dB~']
 
-#ifdef WKV_PROF
-__device__ long long g_prof_bwd[24];   // cycles per phase, summed over the chunks of CTA 0 (profiling builds only)
-#define PROF_MARK(i) do { if (bh == 0 && tid == 0) { const long long now_ = clock64(); g_prof_bwd[i] += now_ - prof_t_; prof_t_ = now_; } } while (0)
-#else
-#define PROF_MARK(i) do { } while (0)
-#endif
 
 // four K=16 steps (64 deep) of D (+)= A B
 __device__ __forceinline__ void mma_k64(uint32_t d, Op a, Op b, uint32_t idesc, bool accumulate) {
@@ -110,7 +104,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
                       __nv_bfloat16* __restrict__ ds0, int* __restrict__ status, int BH, int SEG,
                       float* __restrict__ carry, int* __restrict__ carry_flag, const __grid_constant__ StreamMaps maps,
-                      const unsigned char* __restrict__ saved) {
+                      const unsigned char* __restrict__ saved, const int* __restrict__ residual_mark) {
+    // the forward call fell back to the token-sequential kernel (a decay outside the chunked kernels' range):
+    // the residual is in that kernel's format and its backward, launched behind this one, does the work
+    if (*residual_mark != 0) return;
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -163,9 +160,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     const int si = tid & 63, scq = tid >> 6;   // state element ownership: row si, columns 16scq..16scq+15
     // phase parities: product rounds 1..4 (every chunk), round 0 (recomputing chunks only), staging tiles, saved slabs
     uint32_t par = 0, par0 = 0, spar = 0, lpar = 0;
-#ifdef WKV_PROF
-    long long prof_t_ = clock64();
-#endif
 
     // ---- chunk schedule, walked in reverse.  The extent and the global loads of the next chunk are
     // issued while the tail of the current one (decay-gradient scan) still runs.
@@ -306,9 +300,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     issue_stage(p);
     loaded_next = is_saved(p, n);
     if (loaded_next) issue_saved_late(p);
-#ifdef WKV_PROF
-    prof_t_ = clock64();
-#endif
     while (true) {
         {
             const bool cur_loaded = loaded_next;
@@ -327,7 +318,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     sm.d_in[tid] += acc;
                 }
             }
-            PROF_MARK(0);
             // ---------------- cumulative decay of the chunk ----------------
             float lw[2][8];
 #pragma unroll
@@ -340,7 +330,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
                 *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
             }
-            PROF_MARK(1);
             __syncthreads();
             if (cur_loaded) issue_saved_early(p);   // every thread has emptied the staging tiles over T | A_ak
             if (tid < 128) {
@@ -362,7 +351,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 sm.lam[tid] = ex2(t2);
             }
             __syncthreads();
-            PROF_MARK(2);
             {
                 float h1v[8];
 #pragma unroll
@@ -389,7 +377,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     slab_store(smem + OFF_DD, CB128, t, jb, raw[q][5]);
                 }
             }
-            PROF_MARK(3);
             // ---------------- entering state (bf16) and decayed incoming state gradient (bf16) ----------------
             const float* s0src = reset_here ? nullptr : ((p % kC == 0) ? ckpt + ((size_t)bh * nBlk + p / kC) * kN * kN
                                                                         : s_at_len + st_base);
@@ -418,12 +405,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
-            PROF_MARK(4);
             if (cur_loaded) {
                 // T, A_ak, P_rb, P_rk and sa of this chunk come from the forward
                 if (!tc::mbar_wait(&sm.bar[6], lpar)) failed = true;
                 lpar ^= 1u;
-                PROF_MARK(5);
             } else {
             // ================= R1: Gram blocks, A~ S0^T =================
             if (issuer_a) {
@@ -438,7 +423,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             if (!tc::mbar_wait(&sm.bar[0], par0)) failed = true;
             par0 ^= 1u;
             tc::fence_after_sync();
-            PROF_MARK(5);
             {
                 const int t = row & 63;
                 float d[64];
@@ -464,7 +448,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_before_sync();
             __syncthreads();
             }   // recomputing chunk
-            PROF_MARK(6);
             // ================= R2: G += A_ak V ; [Gd ; dVpart] = [B~;K~] dSL^T + [P_rb|P_rk]^T dY ; inverse =================
             if (issuer_a) {
                 tc::fence_after_sync();
@@ -476,12 +459,10 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 if (!cur_loaded) mma_k64(tbase + T_G, kmaj64(sAAK), mnmaj128(sVSA), ID_KM, true);
                 tc::commit(&sm.bar[1]);
             }
-            PROF_MARK(7);
             if (!cur_loaded) {
                 tri_inverse_64<256>(lf, reinterpret_cast<float*>(smem + OFF_XINV), reinterpret_cast<float*>(smem + OFF_SCR), tid);
                 fp32_to_slab64<256>(reinterpret_cast<const float*>(smem + OFF_XINV), smem + OFF_TINV, CB64, tid);
             }
-            PROF_MARK(8);
             if (quad < 2) {
                 if (!tc::mbar_wait(&sm.bar[1], par)) failed = true;
                 tc::fence_after_sync();
@@ -502,7 +483,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
-            PROF_MARK(9);
             // ================= R3: sa = T G ; dsa = T^T Gd =================
             if (issuer_a) {
                 tc::fence_after_sync();
@@ -533,7 +513,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
-            PROF_MARK(10);
             // ================= R4: dV += A_ak^T dsa ; W = [V;sa][dY;dsa]^T ; tmp = dY^T R~ + dsa^T A~ =================
             if (issuer_a) {
                 tc::fence_after_sync();
@@ -546,7 +525,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 mma_k64(tbase + T_TMP, mnmaj128(sDD + HALF), mnmaj128(sAR), ID_MM, true);
                 tc::commit(&sm.bar[3]);
             }
-            PROF_MARK(11);
             if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
             tc::fence_after_sync();
             // ---------------- plan the next chunk (earlier in time) ----------------
@@ -598,7 +576,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::fence_async_smem();
             tc::fence_before_sync();
             __syncthreads();
-            PROF_MARK(12);
             // ================= R5: [dK~';dB~'] and [dR~';dA~'] =================
             if (issuer_a) {
                 tc::fence_after_sync();
@@ -641,7 +618,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
                 sm.d_part[rq][c] = acc;
             }
-            PROF_MARK(13);
             // everything of the epilogue that does not depend on the products runs while they execute:
             // decay factors of this row and the operand rows it pairs with (kept packed)
             float fx[32], fz[32], lwt[32];
@@ -678,7 +654,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             if (!tc::mbar_wait(&sm.bar[4], par)) failed = true;
             tc::fence_after_sync();
             if (loaded_next) issue_saved_late(p);   // P_rb | P_rk and sa of the next chunk: their hosts are idle now
-            PROF_MARK(14);
             float p3[32];   // a_t da_t for the rows that own da
             {
                 const int t = row & 63;
@@ -715,7 +690,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                         *reinterpret_cast<uint4*>(dz + g + c * 8) = pack8(&z[c * 8]);
                     }
                 }
-            PROF_MARK(15);
                 // u_t = (r dr - k dk) + (a da - b db): first the dk/dr rows write, then the db/da rows add
                 if (row < 64) {
 #pragma unroll
@@ -774,7 +748,6 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&o[c * 8]);
                 }
             }
-            PROF_MARK(16);
             if (cur_reset) {
                 __syncthreads();
 #pragma unroll
@@ -825,27 +798,20 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
 int* wkv7_chunk_status_word();
 
-#ifdef WKV_PROF
-extern "C" int b200wkv_debug_prof_bwd(long long* out, int clear) {
-    long long zero[24] = {};
-    if (cudaMemcpyFromSymbol(out, g_prof_bwd, sizeof(zero)) != cudaSuccess) return -1;
-    if (clear) cudaMemcpyToSymbol(g_prof_bwd, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
-                   const void* ds_out, const void* residual, void* dw, void* dr, void* dk, void* dv, void* da,
-                   void* db, void* ds0) {
+                   const void* ds_out, void* residual, const int* residual_mark, void* dw, void* dr, void* dk, void* dv,
+                   void* da, void* db, void* ds0) {
     typedef __nv_bfloat16 bf;
-    if (cudaFuncSetAttribute(wkv7_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    static DeviceOnce smem_attr;   // the opt-in to large dynamic shared memory is a per-device function attribute
+    if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv7_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); }))
         return B200WKV_ELAUNCH;
     const float* ck = (const float*)residual;
     const int nBlk = (T + kC - 1) / kC;
     const float* sl = ck + (size_t)B * H * nBlk * kN * kN;
     // the tail of the buffer is scratch for carries between CTAs (see chunk_residual_floats)
-    float* carry = const_cast<float*>(ck) + chunk_states_floats(B, T, H);
+    float* carry = (float*)residual + chunk_states_floats(B, T, H);
     int* carry_flag = reinterpret_cast<int*>(carry + (size_t)kHandoffSlots * kHandoffFloats);
     const unsigned char* saved = reinterpret_cast<const unsigned char*>(ck + chunk_saved_offset_floats(B, T, H));
     const bf *pw = (const bf*)w, *pr = (const bf*)r, *pk = (const bf*)k, *pv = (const bf*)v, *pa = (const bf*)a, *pb = (const bf*)b;
@@ -859,12 +825,12 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     // One CTA per SM (shared memory).  With more sequences than SMs the CTAs are persistent; when
     // the sequences do not divide evenly, each is cut into `seg` runs of blocks so that every CTA
     // gets the same number of units, and neighbouring CTAs pass the carry through global memory.
-    const SplitPlan plan = plan_split(BH, nBlk, 1);
+    const SplitPlan plan = plan_split(BH, nBlk, 1, sm_count_of_current_device());
     if (plan.seg > 1) {
         if (cudaMemsetAsync(carry_flag, 0, (size_t)kHandoffSlots * sizeof(int), st) != cudaSuccess) return B200WKV_ELAUNCH;
         int Tl = T, Hl = H, seg = plan.seg;
         void* args[] = {&Tl, &Hl, &pw, &pr, &pk, &pv, &pa, &pb, &length, &ns, &pdy, &pds, &ck, &sl, &gw, &gr, &gk, &gv, &ga,
-                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps, &saved};
+                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps, &saved, &residual_mark};
         // cooperative launch: the runtime guarantees that all CTAs are resident at once, which the
         // carry hand-over relies on; if it refuses, fall through to one CTA per sequence
         if (cudaLaunchCooperativeKernel((const void*)wkv7_chunk_bwd_kernel, dim3(plan.grid), dim3(256), args, SMEM_BYTES, st) ==
@@ -874,7 +840,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     }
     wkv7_chunk_bwd_kernel<<<plan.seg > 1 ? BH : plan.grid, 256, SMEM_BYTES, st>>>(T, H, pw, pr, pk, pv, pa, pb, length, ns, pdy, pds, ck,
                                                                                sl, gw, gr, gk, gv, ga, gb, gs, status, BH, 1,
-                                                                               carry, carry_flag, maps, saved);
+                                                                               carry, carry_flag, maps, saved, residual_mark);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

@@ -27,7 +27,7 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N, const void
                  unsigned flags);
 int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void* w, const void* r, const void* k,
                  const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
-                 const uint8_t* new_starts, const void* dy, const void* ds_out, const void* residual,
+                 const uint8_t* new_starts, const void* dy, const void* ds_out, void* residual,
                  size_t residual_bytes, void* dw, void* dr, void* dk, void* dv, void* da, void* db, void* ds0,
                  unsigned flags);
 }
@@ -36,8 +36,14 @@ namespace {
 
 constexpr size_t kStaticScratchBytes = (size_t)64 << 20;   // 64 MiB per device that loads the library
 
-// File-scope device array: allocated by the CUDA module loader with the library, never by a call.
-// In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
+// File-scope device array: part of this translation unit's device module, not obtained from the
+// allocator by any call.  With CUDA's default lazy module loading the module (and with it the
+// backing of the array) is materialised on a device when the address is first asked for, i.e.
+// inside the first call of the entry point on that device: that first call may therefore take
+// device memory and synchronise, and it fails with B200WKV_ESYMBOL if a framework's pool has
+// already taken all of it.  Make the first call (or set CUDA_MODULE_LOADING=EAGER) before the
+// pool grows.  In host code the name is only a handle for cudaGetSymbolAddress; it is not a
+// device address.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
@@ -51,7 +57,10 @@ int static_scratch_for_current_device(void** out) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (g_scratch_ptr[dev] == nullptr) {
         void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return B200WKV_ELAUNCH;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return B200WKV_ESYMBOL;
+        }
         g_scratch_ptr[dev] = p;
     }
     *out = g_scratch_ptr[dev];
@@ -75,6 +84,11 @@ int b200wkv7_fwd_bwd_static(void* stream, int dtype, int B, int T, int H, int N,
         return b200wkv7_fwd(stream, dtype, B, T, H, N, w, r, k, v, a, b, s0, length, new_starts, y, s_out, nullptr, 0, flags);
     }
     if (need > kStaticScratchBytes) return B200WKV_ESCRATCH;
+    // everything either kernel pair could refuse is checked here, so that a bad argument of the
+    // backward is reported before the forward has been enqueued
+    if (!w || !r || !k || !v || !a || !b || !s0 || !length || !new_starts || !y || !s_out || !dw || !dr || !dk || !dv ||
+        !da || !db || !ds0)
+        return B200WKV_ENULL;
     void* scratch = nullptr;
     int st = static_scratch_for_current_device(&scratch);
     if (st != B200WKV_OK) return st;

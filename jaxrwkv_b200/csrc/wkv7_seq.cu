@@ -8,6 +8,7 @@
 // Semantics: BaseRWKV.inner_loop of jaxrwkv (src/jaxrwkv/rwkv7.py:199-220); the
 // backward is the reverse-time recurrence of the same loop.
 #include "common.cuh"
+#include "device_once.cuh"
 
 namespace b200wkv {
 
@@ -31,7 +32,12 @@ wkv7_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ w, const T* __restric
                     const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ a,
                     const T* __restrict__ b, const T* __restrict__ s0,
                     const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
-                    T* __restrict__ y, T* __restrict__ s_out, float* __restrict__ ckpt) {
+                    T* __restrict__ y, T* __restrict__ s_out, float* __restrict__ ckpt,
+                    const int* __restrict__ run_if, int run_ticket, int* __restrict__ residual_mark) {
+    // As the fallback behind the chunked kernel: run only when that kernel left its ticket in *run_if,
+    // and mark the residual as being in this kernel's format.
+    if (run_if != nullptr && *run_if != run_ticket) return;
+    if (residual_mark != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *residual_mark = 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -171,7 +177,9 @@ wkv7_seq_bwd_kernel(int Tlen, int H, const T* __restrict__ w, const T* __restric
                     const T* __restrict__ dy, const T* __restrict__ ds_out,
                     const float* __restrict__ ckpt,
                     T* __restrict__ dw, T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv,
-                    T* __restrict__ da, T* __restrict__ db, T* __restrict__ ds0) {
+                    T* __restrict__ da, T* __restrict__ db, T* __restrict__ ds0, const int* __restrict__ run_if) {
+    // as the fallback behind the chunked backward: run only when the forward marked the residual as this kernel's
+    if (run_if != nullptr && *run_if == 0) return;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -498,13 +506,15 @@ size_t wkv7_seq_residual_bytes(int B, int T, int H) {
 template <typename T>
 static int launch_fwd(cudaStream_t st, int B, int Tlen, int H, const void* w, const void* r, const void* k,
                       const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
-                      const uint8_t* ns, void* y, void* s_out, void* residual) {
+                      const uint8_t* ns, void* y, void* s_out, void* residual, const int* run_if, int run_ticket,
+                      int* residual_mark) {
     auto kern = wkv7_seq_fwd_kernel<T>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FwdSmem)) != cudaSuccess)
+    static DeviceOnce smem_attr;   // one per template instance; the attribute is per device
+    if (!smem_attr.ok([kern]() { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FwdSmem)); }))
         return B200WKV_ELAUNCH;
     kern<<<B * H, 128, sizeof(FwdSmem), st>>>(Tlen, H, (const T*)w, (const T*)r, (const T*)k, (const T*)v,
                                               (const T*)a, (const T*)b, (const T*)s0, length, ns, (T*)y,
-                                              (T*)s_out, (float*)residual);
+                                              (T*)s_out, (float*)residual, run_if, run_ticket, residual_mark);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
@@ -512,14 +522,15 @@ template <typename T>
 static int launch_bwd(cudaStream_t st, int B, int Tlen, int H, const void* w, const void* r, const void* k,
                       const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
                       const uint8_t* ns, const void* dy, const void* ds_out, const void* residual, void* dw,
-                      void* dr, void* dk, void* dv, void* da, void* db, void* ds0) {
+                      void* dr, void* dk, void* dv, void* da, void* db, void* ds0, const int* run_if) {
     auto kern = wkv7_seq_bwd_kernel<T>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BwdSmem)) != cudaSuccess)
+    static DeviceOnce smem_attr;   // one per template instance; the attribute is per device
+    if (!smem_attr.ok([kern]() { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BwdSmem)); }))
         return B200WKV_ELAUNCH;
     kern<<<B * H, 256, sizeof(BwdSmem), st>>>(Tlen, H, (const T*)w, (const T*)r, (const T*)k, (const T*)v,
                                               (const T*)a, (const T*)b, (const T*)s0, length, ns, (const T*)dy,
                                               (const T*)ds_out, (const float*)residual, (T*)dw, (T*)dr, (T*)dk,
-                                              (T*)dv, (T*)da, (T*)db, (T*)ds0);
+                                              (T*)dv, (T*)da, (T*)db, (T*)ds0, run_if);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
@@ -546,20 +557,23 @@ int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const voi
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
+// run_if / run_ticket / residual_mark: see the kernels; all NULL / 0 for an unconditional call
 int wkv7_seq_fwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w, const void* r, const void* k,
                  const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
-                 const uint8_t* ns, void* y, void* s_out, void* residual) {
-    if (dtype == B200WKV_F32) return launch_fwd<float>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, y, s_out, residual);
-    return launch_fwd<__nv_bfloat16>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, y, s_out, residual);
+                 const uint8_t* ns, void* y, void* s_out, void* residual, const int* run_if, int run_ticket,
+                 int* residual_mark) {
+    if (dtype == B200WKV_F32)
+        return launch_fwd<float>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, y, s_out, residual, run_if, run_ticket, residual_mark);
+    return launch_fwd<__nv_bfloat16>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, y, s_out, residual, run_if, run_ticket, residual_mark);
 }
 
 int wkv7_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* w, const void* r, const void* k,
                  const void* v, const void* a, const void* b, const void* s0, const uint32_t* length,
                  const uint8_t* ns, const void* dy, const void* ds_out, const void* residual, void* dw, void* dr,
-                 void* dk, void* dv, void* da, void* db, void* ds0) {
+                 void* dk, void* dv, void* da, void* db, void* ds0, const int* run_if) {
     if (dtype == B200WKV_F32)
-        return launch_bwd<float>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, dy, ds_out, residual, dw, dr, dk, dv, da, db, ds0);
-    return launch_bwd<__nv_bfloat16>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, dy, ds_out, residual, dw, dr, dk, dv, da, db, ds0);
+        return launch_bwd<float>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, dy, ds_out, residual, dw, dr, dk, dv, da, db, ds0, run_if);
+    return launch_bwd<__nv_bfloat16>(st, B, T, H, w, r, k, v, a, b, s0, length, ns, dy, ds_out, residual, dw, dr, dk, dv, da, db, ds0, run_if);
 }
 
 }  // namespace b200wkv

@@ -8,6 +8,7 @@
 // Same arithmetic as the plain step kernel; jaxrwkv has no kernel here (it falls back to the
 // unrolled Python loop, src/jaxrwkv/rwkv7.py:469-470), the recurrence is rwkv7.py:199-220.
 #include "common.cuh"
+#include "device_once.cuh"
 #include "tc05.cuh"
 
 namespace b200wkv {
@@ -199,22 +200,30 @@ template <typename T>
 int launch(cudaStream_t st, int B, int H, const void* w, const void* r, const void* k, const void* v, const void* a,
            const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y, void* s_out,
            long long s_batch_stride) {
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-            sm_count = 148;
-    }
+    // facts that depend only on (kernel instance, device) are looked up once per device: the shared-memory
+    // opt-in, how many CTAs of this kernel fit an SM, and the address of the device status word
     auto kern = wkv7_step_stream_kernel<T>;
     const int smem = (int)sizeof(StepSmem<T>);
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return B200WKV_ELAUNCH;
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    static DeviceOnce setup;
+    static int per_sm_of[kMaxDevices];
+    static int* status_of[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0) return B200WKV_ELAUNCH;
+    if (!setup.ok([&]() {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return e;
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, smem) != cudaSuccess || n < 1) n = 1;
+            per_sm_of[dev] = n;
+            status_of[dev] = wkv7_chunk_status_word();
+            return cudaSuccess;
+        }))
+        return B200WKV_ELAUNCH;
+    const int sm_count = sm_count_of_current_device(), per_sm = per_sm_of[dev];
     const int BH = B * H;
     const int grid = BH < sm_count * per_sm ? BH : sm_count * per_sm;   // one wave: every CTA resident
     kern<<<grid, 256, smem, st>>>(BH, H, (const T*)w, (const T*)r, (const T*)k, (const T*)v, (const T*)a, (const T*)b,
-                                  (const T*)s0, length, ns, (T*)y, (T*)s_out, wkv7_chunk_status_word(), s_batch_stride);
+                                  (const T*)s0, length, ns, (T*)y, (T*)s_out, status_of[dev], s_batch_stride);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

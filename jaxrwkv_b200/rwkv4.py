@@ -39,8 +39,13 @@ def batched_wkv4_bwd(res, grads, B):
     lib = _lib.load()
     k, v, w_neg, u, s, length, new_starts, residual = res
     gs_new, gy = grads
+    # dense C-order buffers for the kernel (see batched_wkv7_bwd): views and broadcasts are materialised
+    k, v, w_neg, u, s = (x.contiguous() for x in (k, v, w_neg, u, s))
+    length = length.to(device=k.device, dtype=torch.int32).contiguous()
+    new_starts = new_starts.to(device=k.device, dtype=torch.uint8).contiguous()
     code = _lib.dtype_code(k.dtype)
     _, T, C = k.shape
+    assert length.shape == (B,) and new_starts.shape == (B, T)
     gy = None if gy is None else gy.to(k.dtype).contiguous()
     gs_new = None if gs_new is None else gs_new.to(k.dtype).contiguous()
     gk, gv, gs = torch.empty_like(k), torch.empty_like(v), torch.empty_like(s)

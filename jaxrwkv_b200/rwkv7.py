@@ -38,11 +38,13 @@ def _check_inputs(r, w, k, v, a, b, s):
     return _lib.dtype_code(dtype)
 
 
-def batched_wkv7_fwd(r, w, k, v, a, b, s, length, new_starts, B, need_residual=True, flags=0):
+def batched_wkv7_fwd(r, w, k, v, a, b, s, length, new_starts, B, need_residual=True, flags=0, buffers=None):
     """One ``wkv7-fwd`` call on (B,T,H,N) tensors (rwkv7.py:356-376).
 
     Returns ``((new_s, out), residuals)``; ``residuals`` carries the inputs and the
     opaque buffer the backward kernel needs (None when ``need_residual`` is False).
+    ``buffers`` may hold preallocated results ``out``, ``new_s`` and ``residual`` (the way XLA hands a
+    custom call its result buffers); what is missing is allocated here.
     """
     lib = _lib.load()
     code = _check_inputs(r, w, k, v, a, b, s)
@@ -52,33 +54,48 @@ def batched_wkv7_fwd(r, w, k, v, a, b, s, length, new_starts, B, need_residual=T
     length = length.to(device=k.device, dtype=torch.int32).contiguous()      # uint32 bit pattern
     new_starts = new_starts.to(device=k.device, dtype=torch.uint8).contiguous()
     assert length.shape == (B,) and new_starts.shape == (B, T)
-    out = torch.empty_like(k)
-    new_s = torch.empty_like(s)
+    buffers = buffers or {}
+    out = buffers.get("out")
+    new_s = buffers.get("new_s")
+    out = torch.empty_like(k) if out is None else out
+    new_s = torch.empty_like(s) if new_s is None else new_s
     residual, rbytes = None, 0
     if need_residual:
         rbytes = lib.b200wkv7_residual_bytes(code, B, T, H, N)
-        residual = torch.empty(rbytes, dtype=torch.uint8, device=k.device)
+        residual = buffers.get("residual")
+        if residual is None:
+            residual = torch.empty(rbytes, dtype=torch.uint8, device=k.device)
+        elif residual.numel() * residual.element_size() < rbytes or not residual.is_contiguous():
+            raise _lib.B200WKVError("wkv7: the preallocated residual is too small")
     _lib.check(lib.b200wkv7_fwd(_stream(), code, B, T, H, N, _ptr(w), _ptr(r), _ptr(k), _ptr(v), _ptr(a), _ptr(b),
                                 _ptr(s), _ptr(length), _ptr(new_starts), _ptr(out), _ptr(new_s),
                                 _ptr(residual), rbytes, flags))
     return (new_s, out), (r, w, k, v, a, b, s, length, new_starts, residual)
 
 
-def batched_wkv7_bwd(res, grads, B, flags=0):
+def batched_wkv7_bwd(res, grads, B, flags=0, buffers=None):
     """One ``wkv7-bwd`` call (rwkv7.py:378-411).  ``grads`` is ``(gs_out, gy)``; either may be
-    None.  Returns ``(gr, gw, gk, gv, ga, gb, gs)`` in the operator's argument order."""
+    None.  Returns ``(gr, gw, gk, gv, ga, gb, gs)`` in the operator's argument order.  ``buffers`` may
+    hold preallocated results under those seven names."""
     lib = _lib.load()
     r, w, k, v, a, b, s, length, new_starts, residual = res
     gs_out, gy = grads
+    # the kernels read dense C-order buffers: a vmapped axis moved to the front, a permuted view or a
+    # broadcast (stride-0) length / new_starts must be materialised exactly as the forward does
+    r, w, k, v, a, b, s = (x.contiguous() for x in (r, w, k, v, a, b, s))
+    length = length.to(device=k.device, dtype=torch.int32).contiguous()
+    new_starts = new_starts.to(device=k.device, dtype=torch.uint8).contiguous()
     code = _lib.dtype_code(k.dtype)
     _, T, H, N = k.shape
+    assert length.shape == (B,) and new_starts.shape == (B, T)
     gy = None if gy is None else gy.to(k.dtype).contiguous()
     gs_out = None if gs_out is None else gs_out.to(k.dtype).contiguous()
-    gw, gr, gk, gv, ga, gb = (torch.empty_like(k) for _ in range(6))
-    gs = torch.empty_like(s)
+    buffers = buffers or {}
+    gw, gr, gk, gv, ga, gb = (buffers[n] if n in buffers else torch.empty_like(k) for n in ("gw", "gr", "gk", "gv", "ga", "gb"))
+    gs = buffers["gs"] if "gs" in buffers else torch.empty_like(s)
     _lib.check(lib.b200wkv7_bwd(_stream(), code, B, T, H, N, _ptr(w), _ptr(r), _ptr(k), _ptr(v), _ptr(a), _ptr(b),
                                 _ptr(s), _ptr(length), _ptr(new_starts), _ptr(gy), _ptr(gs_out),
-                                _ptr(residual), residual.numel(), _ptr(gw), _ptr(gr), _ptr(gk), _ptr(gv),
+                                _ptr(residual), residual.numel() * residual.element_size(), _ptr(gw), _ptr(gr), _ptr(gk), _ptr(gv),
                                 _ptr(ga), _ptr(gb), _ptr(gs), flags))
     return gr, gw, gk, gv, ga, gb, gs
 

@@ -111,3 +111,44 @@ def test_config3_full_size_properties():
     so, yo = oracle.wkv6_base(*[x[bi][:, hh:hh + 1].double().cpu().numpy() for x in (r, k, v, w)], u[hh:hh + 1].double().cpu().numpy(),
                               s0[bi][hh:hh + 1].double().cpu().numpy(), T, ns[bi].cpu().numpy(), "6")
     assert rel_err(npf(y[bi][:, hh:hh + 1]), yo) < 2e-2 and rel_err(npf(s[bi][hh:hh + 1]), so) < 2e-2
+
+
+def test_config3_full_size_backward():
+    """Config 3 exactly (B=16, T=4096, H=32, bf16, starts p=1/512, s0 ~ N(0, 0.1), dy and dstate ~ N(0,1)):
+    forward + backward through the operator; gradients finite, deterministic and homogeneous of degree one in
+    the cotangents; four (batch, head) slices against the oracle's reverse loop (du, a sum over the batch,
+    against the oracle on those slices is not separable and is checked at small sizes instead)."""
+    B, T, H = 16, 4096, 32
+    g = torch.Generator(device="cuda").manual_seed(1236)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    r, k, v = (rn(B, T, H, 64).bfloat16() for _ in range(3))
+    w = (-torch.exp(-0.5 + 0.5 * rn(B, T, H, 64))).bfloat16().unsqueeze(-1)
+    u = (0.1 * rn(H, 64, 1)).bfloat16()
+    s0 = (0.1 * rn(B, H, 64, 64)).bfloat16()
+    ns = torch.rand(B, T, generator=g, device="cuda") < 1 / 512
+    length = torch.full((B,), T, device="cuda")
+    gy, gs = rn(B, T, H, 64).bfloat16(), rn(B, H, 64, 64).bfloat16()
+
+    def grads(scale):
+        leaves = [x.clone().requires_grad_(True) for x in (r, k, v, w, u, s0)]
+        s, y = rwkv6.CudaRWKV.inner_loop(*leaves, length, ns)
+        torch.autograd.backward((y, s), (gy * scale, gs * scale))
+        return [x.grad for x in leaves]
+
+    g1, g1b, g2 = grads(1), grads(1), grads(2)
+    for n, a, b, c in zip(("dr", "dk", "dv", "dw", "du", "ds0"), g1, g1b, g2):
+        assert torch.isfinite(a.float()).all(), n
+        assert torch.equal(a, b), n
+        if n != "du":                      # du is rounded to bf16 after the sum over the batch
+            assert torch.equal(c, a * 2), n
+    f64 = lambda x: x.double().cpu().numpy()
+    for bi, hh in ((0, 0), (3, 17), (9, 5), (15, 31)):
+        ins = [f64(x[bi:bi + 1, :, hh:hh + 1]) for x in (r, k, v, w)] + [f64(u[hh:hh + 1]), f64(s0[bi:bi + 1, hh:hh + 1])]
+        ref = oracle.wkv6_bwd_batched(*ins, np.array([T], dtype=np.uint32), ns[bi:bi + 1].cpu().numpy(),
+                                      f64(gy[bi:bi + 1, :, hh:hh + 1]), f64(gs[bi:bi + 1, hh:hh + 1]), "6")
+        got = [g1[0][bi:bi + 1, :, hh:hh + 1], g1[1][bi:bi + 1, :, hh:hh + 1], g1[2][bi:bi + 1, :, hh:hh + 1],
+               g1[3][bi:bi + 1, :, hh:hh + 1], None, g1[5][bi:bi + 1, hh:hh + 1]]
+        for n, a, b in zip(("dr", "dk", "dv", "dw", "du", "ds0"), got, ref):
+            if a is not None:
+                e = rel_err(npf(a).reshape(b.shape), b)
+                assert e < 2e-2, (n, bi, hh, e)

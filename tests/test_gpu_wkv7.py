@@ -156,6 +156,59 @@ def test_operator_autograd_and_vmap_on_gpu():
     assert torch.equal(y2[0], y2[1]) and torch.equal(y2[0], y2[2]) and torch.equal(s2[0], s2[2])
 
 
+def _residual_mark(res):
+    """Last word pair of the bf16 residual: 0 = written by the chunked kernel, 1 = by the sequential fallback."""
+    return int(res[-1][-16:].view(torch.int32)[0].item())
+
+
+def test_decay_outside_the_chunked_range_is_still_exact_bf16():
+    """BaseRWKV.inner_loop (rwkv7.py:201) applies exp(-exp(w)) to ANY w.  With w up to 2 the decay reaches
+    6e-4 per token, and the cumulative decay inside a 64-token chunk leaves what the tensor-core products can
+    carry; the forward must notice, and both directions must still match the oracle - without the caller
+    asking for the sequential kernels."""
+    d = wkv7_case(2, 200, 2, seed=77, s0_scale=0.5, starts=[[0, 90], []], lengths=[200, 150])
+    d["w"] = np.random.default_rng(5).uniform(-0.5, 2.0, size=d["w"].shape).astype(np.float32)
+    check_fwd(d, torch.bfloat16)
+    check_bwd(d, torch.bfloat16)
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    assert _residual_mark(run_fwd(t, length, ns)[2]) == 1
+    # the model's own parametrisation (w <= -0.5) stays on the tensor-core kernels
+    d2 = wkv7_case(2, 200, 2, seed=78, s0_scale=0.5)
+    t2 = to_dev(d2, torch.bfloat16)
+    length2, ns2 = flags(d2)
+    assert _residual_mark(run_fwd(t2, length2, ns2)[2]) == 0
+    # only one sequence of the batch out of range, inference call (no residual)
+    d3 = wkv7_case(3, 130, 2, seed=79, s0_scale=0.5)
+    d3["w"][1, 40:60] = 2.5
+    t3 = to_dev(d3, torch.bfloat16)
+    length3, ns3 = flags(d3)
+    (s, y), _ = rwkv7.batched_wkv7_fwd(*[t3[n] for n in NAMES7], length3, ns3, 3, need_residual=False)
+    so, yo = oracle.wkv7_base_batched(*rounded(t3), d3["length"], d3["new_starts"])
+    assert rel_err(npf(y), yo) < TOL[torch.bfloat16] and rel_err(npf(s), so) < TOL[torch.bfloat16]
+
+
+def test_operator_backward_with_strided_and_broadcast_operands():
+    """Gradients through views the kernels cannot read directly: the vmapped axis in position 1
+    (moved to the front as a strided view) and one int32 length / uint8 new_starts row shared by the
+    whole batch (a stride-0 broadcast).  Both must give the oracle's gradients."""
+    B, T, H = 3, 40, 2
+    d = wkv7_case(B, T, H, seed=33, s0_scale=0.5, starts=[[0, 17]] * B, lengths=[29] * B)
+    t = to_dev(d, torch.float32)
+    # (T, B, H, N) storage, vmapped over axis 1; the state is (H, B, N, N), vmapped over axis 1
+    leaves = [t[n].movedim(0, 1).contiguous().requires_grad_(True) for n in NAMES7]
+    length = torch.tensor(29, dtype=torch.int32).cuda()
+    ns = torch.tensor(d["new_starts"][0]).to(torch.uint8).cuda()
+    s, y = torch.vmap(rwkv7.CudaRWKV.inner_loop, in_dims=(1,) * 7 + (None, None))(*leaves, length, ns)
+    gy, gs = torch.randn_like(y), torch.randn_like(s)
+    ((y * gy).sum() + (s * gs).sum()).backward()
+    ref = oracle.wkv7_bwd_batched(*rounded(t), d["length"], d["new_starts"], npf(gy), npf(gs))
+    so, yo = oracle.wkv7_base_batched(*rounded(t), d["length"], d["new_starts"])
+    assert rel_err(npf(y), yo) < 1e-4 and rel_err(npf(s), so) < 1e-4
+    for n, leaf, g in zip(NAMES7, leaves, ref):
+        assert rel_err(npf(leaf.grad.movedim(1, 0)), g) < 1e-4, n
+
+
 @pytest.mark.parametrize("dtype,kflags", KERNELS)
 def test_run_to_run_determinism(dtype, kflags):
     d = wkv7_case(2, 100, 2, seed=31, p_start=0.05, s0_scale=0.3)
@@ -306,6 +359,12 @@ def test_chunk_fwd_full_size_properties():
     # sequential kernel on the same inputs
     s_q, y_q, _ = run_fwd(t, length, ns, _lib.FLAG_SEQUENTIAL)
     assert rel_err(npf(y), npf(y_q)) < TOL[torch.bfloat16] and rel_err(npf(s), npf(s_q)) < TOL[torch.bfloat16]
+    # and the oracle itself on four (batch, head) slices: y and the returned state
+    for bi, hh in ((0, 0), (2, 9), (5, 30), (7, 31)):
+        ins = [t[n][bi, :, hh:hh + 1].double().cpu().numpy() for n in NAMES7[:-1]] + [t["s0"][bi, hh:hh + 1].double().cpu().numpy()]
+        so, yo = oracle.wkv7_base(*ins, int(d["length"][bi]), d["new_starts"][bi])
+        assert rel_err(npf(y[bi, :, hh:hh + 1]), yo) < TOL[torch.bfloat16], ("y", bi, hh)
+        assert rel_err(npf(s[bi, hh:hh + 1]), so) < TOL[torch.bfloat16], ("s_out", bi, hh)
 
 
 def test_chunk_bwd_full_size_properties():
