@@ -26,8 +26,13 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                    void* s_out, void* residual, int* residual_mark, int** range_flag, int* range_ticket);
 int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
-                   const void* ds_out, void* residual, const int* residual_mark, void* dw, void* dr, void* dk, void* dv,
-                   void* da, void* db, void* ds0);
+                   const void* ds_out, void* residual, const int* residual_mark, const int* fast, void* dw, void* dr,
+                   void* dk, void* dv, void* da, void* db, void* ds0);
+int wkv7_carry_bwd(cudaStream_t st, int B, int T, int H, const uint32_t* length, const uint8_t* ns, const void* dy,
+                   const void* ds_out, void* residual, const int* residual_mark, void* ds0);
+int wkv7_grad_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
+                  const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy, void* residual,
+                  const int* residual_mark, void* dw, void* dr, void* dk, void* dv, void* da, void* db);
 int wkv7_chunk_status();
 
 size_t wkv6_seq_residual_bytes(int B, int T, int H);
@@ -141,8 +146,19 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void
     // must match the kernel family that filled the residual in b200wkv7_fwd (same dtype and flags)
     if (dtype == B200WKV_BF16 && !(flags & B200WKV_FLAG_SEQUENTIAL)) {
         const int* mark = residual_mark_of(residual, b200wkv7_residual_bytes(dtype, B, T, H, N));
+        const int* fast = reinterpret_cast<const int*>(static_cast<const char*>(residual) + carry_layout(B, T, H).fast);
+        if (T % kC == 0) {
+            // sequences the forward walked in full saved blocks: the sequential state-gradient carry, then the
+            // gradients of all blocks in parallel
+            st = wkv7_carry_bwd((cudaStream_t)stream, B, T, H, length, new_starts, dy, ds_out, residual, mark, ds0);
+            if (st != B200WKV_OK) return st;
+            st = wkv7_grad_bwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, length, new_starts, dy, residual, mark, dw, dr, dk,
+                               dv, da, db);
+            if (st != B200WKV_OK) return st;
+        }
+        // every other sequence (start flags or `length` inside a block, ragged T): the one-kernel backward
         st = wkv7_chunk_bwd((cudaStream_t)stream, B, T, H, w, r, k, v, a, b, length, new_starts, dy, ds_out, residual, mark,
-                            dw, dr, dk, dv, da, db, ds0);
+                            fast, dw, dr, dk, dv, da, db, ds0);
         if (st != B200WKV_OK) return st;
         return wkv7_seq_bwd((cudaStream_t)stream, dtype, B, T, H, w, r, k, v, a, b, s0, length, new_starts, dy, ds_out,
                             residual, dw, dr, dk, dv, da, db, ds0, mark);

@@ -27,19 +27,46 @@ constexpr int kHandoffFloats = kN * kN + kN;
 inline size_t chunk_states_floats(int B, int T, int H) {
     return (size_t)B * H * ((size_t)((T + kC - 1) / kC) + 1) * kN * kN;
 }
-//   [B*H][ceil(T/64)][6 slabs]  for every 64-token block that the forward walked as ONE chunk: the bf16
-//                               operand slabs T = (I - A_ab)^-1, A_ak, P_rb, P_rk, sa and the entering state S0
+//   [B*H][ceil(T/64)][6 tiles]  for every 64-token block that the forward walked as ONE chunk: the bf16
+//                               operands T = (I - A_ab)^-1, A_ak, P_rb, P_rk, sa and the entering state S0
 //                               exactly as the forward used them, so the backward loads them instead of
-//                               recomputing them
-constexpr int kSavedSlabs = 6;   // order: T, A_ak, P_rb, P_rk, sa, S0 (64-row slabs)
+//                               recomputing them.  A tile is 8 column blocks of [64 rows][16 bytes] (the
+//                               operand slab layout without the shared-memory padding), 8 KB.
+constexpr int kSavedSlabs = 6;   // order: T, A_ak, P_rb, P_rk, sa, S0
 constexpr int SAVED_T = 0, SAVED_AAK = 1, SAVED_PRB = 2, SAVED_PRK = 3, SAVED_SA = 4, SAVED_S0 = 5;
-constexpr size_t kSavedBytes = (size_t)kSavedSlabs * SLAB64;
+constexpr int GCB = kC * 16;          // column-block pitch of a tile in global memory (1024)
+constexpr int GTILE = 8 * GCB;        // 8192
+constexpr size_t kSavedBytes = (size_t)kSavedSlabs * GTILE;
 inline size_t chunk_saved_offset_floats(int B, int T, int H) {
     return chunk_states_floats(B, T, H) + (size_t)kHandoffSlots * (kHandoffFloats + 1);
 }
-inline size_t chunk_residual_floats(int B, int T, int H) {
-    return chunk_saved_offset_floats(B, T, H) + (size_t)B * H * ((T + kC - 1) / kC) * (kSavedBytes / sizeof(float));
+// What the carry / gradient split of the backward adds behind the saved tiles (see wkv7_carry.cu, wkv7_grad.cu):
+//   [B*H][ceil(T/64)][64][64] bf16  M' = W~^T B^ of every saved block: S_C = S0 diag(L_C) + S0 M' + (terms without S0)
+//   [B*T][H*64]               bf16  R- = R~ + P_rb W~ (token rows, laid out like the streams): y_t = R-_t S0^T + ...
+//   [B*H][ceil(T/64)][64]     fp32  L_C, the decay over the whole block
+//   [B*H][ceil(T/64)][64][64] bf16  scratch of the backward: the state gradient leaving every block
+//   [B*H]                     int   1 if the forward walked the whole sequence as full, saved blocks
+//   [kGradCtas][4][64][64]    bf16  scratch of the gradient kernel, one set per CTA: the decay factors 1/L_t, L_t,
+//                                   L_{t-1} and the log-decay of the block in hand (written when the operands are
+//                                   scaled, read back by the last epilogue; it lives in L2)
+constexpr int kGradCtas = 512;
+struct CarryLayout {
+    size_t mprime, rbar, lam, dstate, fast, fscr, end;   // byte offsets from the start of the residual
+};
+inline CarryLayout carry_layout(int B, int T, int H) {
+    const size_t nBlk = (size_t)((T + kC - 1) / kC), BH = (size_t)B * H;
+    CarryLayout l;
+    l.mprime = (chunk_saved_offset_floats(B, T, H)) * sizeof(float) + BH * nBlk * kSavedBytes;
+    l.rbar = l.mprime + BH * nBlk * GTILE;
+    l.lam = l.rbar + (size_t)B * nBlk * kC * H * kN * 2;      // token rows padded to whole blocks
+    l.dstate = l.lam + BH * nBlk * kN * sizeof(float);
+    l.fast = l.dstate + BH * nBlk * GTILE;
+    l.fscr = (l.fast + BH * sizeof(int) + 255) / 256 * 256;
+    const size_t ctas = BH * nBlk < (size_t)kGradCtas ? BH * nBlk : (size_t)kGradCtas;
+    l.end = l.fscr + ctas * 4 * GTILE;
+    return l;
 }
+inline size_t chunk_residual_floats(int B, int T, int H) { return carry_layout(B, T, H).end / sizeof(float); }
 
 // Host side of the split: grid size and segments per sequence for `chains` sequences of `n_blk`
 // blocks with `per_sm` resident CTAs per SM on a device of `sm_count` SMs (the launchers pass the

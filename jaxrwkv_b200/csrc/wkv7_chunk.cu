@@ -87,7 +87,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
                       __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
                       const __grid_constant__ StreamMaps maps, unsigned char* __restrict__ saved,
-                      int* __restrict__ range_flag, int range_ticket, int* __restrict__ residual_mark) {
+                      int* __restrict__ range_flag, int range_ticket, int* __restrict__ residual_mark,
+                      __nv_bfloat16* __restrict__ mprime, __nv_bfloat16* __restrict__ rbar, float* __restrict__ lam_out,
+                      int* __restrict__ fast_flag) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -102,7 +104,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 5; ++i) tc::mbar_init(&sm.bar[i], 1);
+        for (int i = 0; i < 5; ++i) tc::mbar_init(&sm.bar[i], (i == 2 || i == 3) ? 2 : 1);   // M3, M4: two issuing threads
         tc::mbar_init_fence();
         if (bh == 0 && residual_mark != nullptr) *residual_mark = 0;   // this residual is in the chunked format (so far)
     }
@@ -145,7 +147,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     float* scr = reinterpret_cast<float*>(smem + OFF_SCR);
     const int tsub = tid >> 3, jb = tid & 7;                // staging unit: tokens 32q+tsub (q=0,1), channels 8jb..8jb+7
 
+    constexpr int kIssuer2 = 96;   // a thread of the warp with the least epilogue work
     int p = 0;
+    bool all_saved = (saved != nullptr);   // every chunk so far was a full block with its operands saved
     uint32_t par = 0, spar = 0;   // phase parities of the product barriers and of the staging barrier
     uint8_t flag_ahead = (tid < 64 && tid < Tlen) ? new_starts[(size_t)bi * Tlen + tid] : 0;
     // the 64 token rows from cp on of w, r, k, v, a, b into the staging tiles (thread 0; one tiled copy
@@ -192,6 +196,8 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         // a block walked as one full chunk leaves its operand slabs T, A_ak, P_rb, P_rk, sa for the backward
         unsigned char* const keep = (saved != nullptr && n == kC && (p & (kC - 1)) == 0)
                                         ? saved + ((size_t)bh * nBlk + (p >> 6)) * kSavedBytes : nullptr;
+        all_saved = all_saved && (keep != nullptr);
+        const size_t blk_slot = (size_t)bh * nBlk + (p >> 6);
         // the fp32 state entering a block is only needed by a backward that recomputes the block's first chunk,
         // i.e. when that chunk is short; a full chunk passes its bf16 entering state with the saved slabs
         if (quad < 2 && ckpt != nullptr && (p & (kC - 1)) == 0 && n < kC) {
@@ -272,8 +278,16 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     eE[e] = lamv[e] * eI[e];   // 2^(total - cc) without a fourth trip to the special-function unit
                 }
                 // raw: r, k, v, a, b
-                slab_store(smem + OFF_AR, CB128, t, jb, scale8(raw[q][3], eP));
-                slab_store(smem + OFF_AR, CB128, 64 + t, jb, scale8(raw[q][0], eL));
+                const uint4 a_t = scale8(raw[q][3], eP), r_t = scale8(raw[q][0], eL);
+                slab_store(smem + OFF_AR, CB128, t, jb, a_t);
+                slab_store(smem + OFF_AR, CB128, 64 + t, jb, r_t);
+                if (keep != nullptr) {
+                    // W~ = T A~ is formed after the inverse, when the [A~ ; R~] slab has long been written over:
+                    // a second copy of A~ waits in the sa slab, which is idle until sa itself is stored; R~ goes
+                    // to the R- rows in global memory, where P_rb W~ is added at the end of the chunk
+                    slab_store(smem + OFF_SA, CB64, t, jb, a_t);
+                    *reinterpret_cast<uint4*>(rbar + seq_base + (size_t)(p + t) * tok_stride + jb * 8) = r_t;
+                }
                 slab_store(smem + OFF_BK, CB128, t, jb, scale8(raw[q][4], eI));
                 slab_store(smem + OFF_BK, CB128, 64 + t, jb, scale8(raw[q][1], eI));
                 slab_store(smem + OFF_BH, CB64, t, jb, scale8(raw[q][4], eE));
@@ -311,10 +325,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             mma_k64(tbase + D2, kmaj128(sAR), kmaj64(sS0), ID_128x64_KK, false);
             tc::commit(&sm.bar[0]);
         }
-        if (keep != nullptr && tid == 7 * 32) {   // the bf16 entering state goes to the residual as it is
-            tc::bulk_store(keep + (size_t)SAVED_S0 * SLAB64, smem + OFF_S0, SLAB64);
+        if (keep != nullptr && warp == 7 && lane < 8) {   // the bf16 entering state goes to the residual as it is
+            tc::bulk_store(keep + (size_t)SAVED_S0 * GTILE + lane * GCB, smem + OFF_S0 + lane * CB64, 64 * 16);
             tc::bulk_commit();
         }
+        if (keep != nullptr && tid < 64) lam_out[blk_slot * kN + tid] = sm.lam[tid];
         if (!tc::mbar_wait(&sm.bar[0], par)) failed = true;
         tc::fence_after_sync();
         // ================= E1: triangular masks, operands of the next products =================
@@ -356,7 +371,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         if (keep != nullptr && warp == 7 && lane < 24) {
             const int which = lane >> 3, c = lane & 7;   // 0: A_ak, 1: P_rk, 2: P_rb
             const unsigned char* src = smem + (which == 2 ? OFF_TP : OFF_M2A) + c * CB128 + (which == 0 ? 0 : 64 * 16);
-            unsigned char* dst = keep + (size_t)(which == 0 ? SAVED_AAK : (which == 1 ? SAVED_PRK : SAVED_PRB)) * SLAB64 + c * CB64;
+            unsigned char* dst = keep + (size_t)(which == 0 ? SAVED_AAK : (which == 1 ? SAVED_PRK : SAVED_PRB)) * GTILE + c * GCB;
             tc::bulk_store(dst, src, 64 * 16);
             tc::bulk_commit();
         }
@@ -375,13 +390,17 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         tc::fence_before_sync();
         __syncthreads();
         if (keep != nullptr && warp == 7 && lane < 8) {   // T: rows 0..63 of the [Tinv ; P_rb] slab
-            tc::bulk_store(keep + (size_t)SAVED_T * SLAB64 + lane * CB64, smem + OFF_TP + lane * CB128, 64 * 16);
+            tc::bulk_store(keep + (size_t)SAVED_T * GTILE + lane * GCB, smem + OFF_TP + lane * CB128, 64 * 16);
             tc::bulk_commit();
         }
         // ================= M3: sa = Tinv G =================
         if (tid == 0) {
             tc::fence_after_sync();
             mma_k64(tbase + D1, kmaj128(sTP), mnmaj64(sG), ID_128x64_KM, false);
+            tc::commit(&sm.bar[2]);
+        } else if (tid == kIssuer2) {   // what only the backward's carry needs is issued by a second thread
+            tc::fence_after_sync();
+            if (keep != nullptr) mma_k64(tbase + D1 + 64, kmaj128(sTP), mnmaj64(sSA), ID_128x64_KM, false);   // W~ = Tinv A~
             tc::commit(&sm.bar[2]);
         }
         // the rows of the next chunk start travelling: their tiles lie over buffers that are idle from
@@ -395,12 +414,18 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::tmem_wait_ld();
 #pragma unroll
             for (int c = 0; c < 4; ++c) slab_store(smem + OFF_SA, CB64, row, hsel * 4 + c, pack8(&sa[c * 8]));
+            if (keep != nullptr) {
+                tc::tmem_ld32(lane_addr + D1 + 64 + hsel * 32, sa);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) slab_store(smem + OFF_G, CB64, row, hsel * 4 + c, pack8(&sa[c * 8]));
+            }
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
-        if (keep != nullptr && tid == 7 * 32) {   // sa: the slab as it is (column-block padding included)
-            tc::bulk_store(keep + (size_t)SAVED_SA * SLAB64, smem + OFF_SA, SLAB64);
+        if (keep != nullptr && warp == 7 && lane < 8) {   // sa
+            tc::bulk_store(keep + (size_t)SAVED_SA * GTILE + lane * GCB, smem + OFF_SA + lane * CB64, 64 * 16);
             tc::bulk_commit();
         }
         // ================= M4: Y += P_rb sa ; S += sa^T B^ + V^T K^ =================
@@ -410,8 +435,23 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             mma_k64(tbase + DS, mnmaj64(sSA), mnmaj64(sBH), ID_128x64_MM, true);
             mma_k64(tbase + DS, mnmaj64(sV), mnmaj64(sKH), ID_128x64_MM, true);
             tc::commit(&sm.bar[3]);
+        } else if (tid == kIssuer2) {
+            tc::fence_after_sync();
+            if (keep != nullptr) {
+                // the transition's off-diagonal part M' = W~^T B^ (rows 0..63 of the accumulator are used) and
+                // the state-dependent part of the outputs, P_rb W~ (rows 64..127)
+                mma_k64(tbase + D1, mnmaj64(sG), mnmaj64(sBH), ID_128x64_MM, false);
+                mma_k64(tbase + D1 + 64, kmaj128(sTP), mnmaj64(sG), ID_128x64_KM, false);
+            }
+            tc::commit(&sm.bar[3]);
         }
         if (tid < 64) flag_ahead = (p1 + tid < Tlen) ? new_starts[(size_t)bi * Tlen + p1 + tid] : 0;   // next chunk's start flags
+        uint4 r_old[4];   // the R~ row stored at the start of the chunk, asked for while the products run
+        if (keep != nullptr && quad >= 2) {
+            const __nv_bfloat16* src = rbar + seq_base + (size_t)(p + row - 64) * tok_stride + hsel * 32;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) r_old[c] = *reinterpret_cast<const uint4*>(src + c * 8);
+        }
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
         if (quad >= 2) {
@@ -425,11 +465,35 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&yv[c * 8]);
             }
         }
+        if (keep != nullptr) {
+            float m[32];
+            if (quad < 2) {       // M'[j][j'], row j = this thread's lane
+                tc::tmem_ld32(lane_addr + D1 + hsel * 32, m);
+                tc::tmem_wait_ld();
+                __nv_bfloat16* dst = mprime + (blk_slot * kN + row) * kN + hsel * 32;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&m[c * 8]);
+            } else {              // R-_t = R~_t + (P_rb W~)_t on top of the R~ row stored at the start of the chunk
+                const int t = row - 64;
+                tc::tmem_ld32(lane_addr + D1 + 64 + hsel * 32, m);
+                tc::tmem_wait_ld();
+                __nv_bfloat16* dst = rbar + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float old[8];
+                    unpack8(r_old[c], old);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) old[e] += m[c * 8 + e];
+                    *reinterpret_cast<uint4*>(dst + c * 8) = pack8(old);
+                }
+            }
+        }
         tc::fence_before_sync();
         if (warp == 7) tc::bulk_wait_read<0>();   // the slabs copied out may be rewritten after the next barrier
         p = p1;
         par ^= 1u;
     }
+    if (fast_flag != nullptr && tid == 0) fast_flag[bh] = all_saved ? 1 : 0;
     if (warp == 7) tc::bulk_wait_all<0>();   // every copy to the residual has landed before the CTA retires
     if (failed) atomicExch(&g_status, 1);
     tc::fence_before_sync();
@@ -474,6 +538,7 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     const unsigned ticket = tickets.fetch_add(1);
     *range_flag = ring + (ticket & 63u);
     *range_ticket = (int)(ticket | 0x40000000u);   // never 0, so untouched memory cannot match
+    const CarryLayout lay = carry_layout(B, T, H);
     StreamMaps maps;
     const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]
     if (!make_stream_maps(&maps, bases, 6, B, T, H)) return B200WKV_ELAUNCH;
@@ -483,7 +548,11 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                                                           residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
                                                           maps,
                                                           residual ? (unsigned char*)((float*)residual + chunk_saved_offset_floats(B, T, H)) : nullptr,
-                                                          *range_flag, *range_ticket, residual_mark);
+                                                          *range_flag, *range_ticket, residual_mark,
+                                                          residual ? (bf*)((char*)residual + lay.mprime) : nullptr,
+                                                          residual ? (bf*)((char*)residual + lay.rbar) : nullptr,
+                                                          residual ? (float*)((char*)residual + lay.lam) : nullptr,
+                                                          residual ? (int*)((char*)residual + lay.fast) : nullptr);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

@@ -104,10 +104,19 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
                       __nv_bfloat16* __restrict__ ds0, int* __restrict__ status, int BH, int SEG,
                       float* __restrict__ carry, int* __restrict__ carry_flag, const __grid_constant__ StreamMaps maps,
-                      const unsigned char* __restrict__ saved, const int* __restrict__ residual_mark) {
+                      const unsigned char* __restrict__ saved, const int* __restrict__ residual_mark,
+                      const int* __restrict__ fast) {
     // the forward call fell back to the token-sequential kernel (a decay outside the chunked kernels' range):
     // the residual is in that kernel's format and its backward, launched behind this one, does the work
     if (*residual_mark != 0) return;
+    // sequences walked in full saved blocks belong to the carry + gradient kernels; leave at once (before any
+    // barrier or TMEM allocation) when nothing else lies in this CTA's range
+    {
+        const long long lo = (long long)BH * SEG * blockIdx.x / gridDim.x, hi = (long long)BH * SEG * (blockIdx.x + 1) / gridDim.x;
+        bool mine = false;
+        for (long long c = lo / SEG; c <= (hi - 1) / SEG && hi > lo; ++c) mine = mine || (fast[c] == 0);
+        if (!mine) return;
+    }
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -233,28 +242,38 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     // P_rb|P_rk and sa can start as soon as the fifth product round of the chunk before has completed;
     // T|A_ak lie under staging tiles and follow once take_stage has emptied those.
     auto is_saved = [&](int cp, int cn) { return cn == kC && (cp & (kC - 1)) == 0; };
+    // Tiles in global memory are unpadded (8 column blocks of 1 KB); the slabs here are padded, so every tile
+    // arrives as 8 copies, one per column block, issued by the lanes of one warp.
     auto issue_saved_late = [&](int cp) {
-        if (tid == kSavedThread) {
+        if (warp == (kSavedThread >> 5)) {
             const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
-            tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(5 * SLAB64 + kC * kN * 2));
-            tc::bulk_load(smem + OFF_PRB, src + SAVED_PRB * SLAB64, 2 * SLAB64, &sm.bar[6]);
-            tc::bulk_load(smem + OFF_S0, src + SAVED_S0 * SLAB64, SLAB64, &sm.bar[6]);
-            tc::bulk_prefetch_l2(src + SAVED_T * SLAB64, 2 * SLAB64);   // copied in later, from L2 then
-#pragma unroll
-            for (int c = 0; c < 8; ++c)   // sa: rows 64..127 of the [V ; sa] slab, one column block at a time
-                tc::bulk_load(smem + OFF_VSA + c * CB128 + 64 * 16, src + SAVED_SA * SLAB64 + c * CB64, 64 * 16, &sm.bar[6]);
+            if (lane == 0) {
+                tc::mbar_expect_tx(&sm.bar[6], (uint32_t)(6 * GTILE));
+                tc::bulk_prefetch_l2(src + SAVED_T * GTILE, 2 * GTILE);   // copied in later, from L2 then
+            }
+            __syncwarp();
+            const int c = lane & 7, which = lane >> 3;   // 0: P_rb, 1: P_rk, 2: S0, 3: sa
+            const int tile = which == 0 ? SAVED_PRB : (which == 1 ? SAVED_PRK : (which == 2 ? SAVED_S0 : SAVED_SA));
+            unsigned char* dst = which == 0 ? smem + OFF_PRB + c * CB64
+                               : which == 1 ? smem + OFF_PRK + c * CB64
+                               : which == 2 ? smem + OFF_S0 + c * CB64
+                                            : smem + OFF_VSA + c * CB128 + 64 * 16;
+            tc::bulk_load(dst, src + (size_t)tile * GTILE + c * GCB, 64 * 16, &sm.bar[6]);
         }
     };
     auto issue_saved_early = [&](int cp) {
-        if (tid == kSavedThread) {
+        if (warp == (kSavedThread >> 5) && lane < 16) {
             const unsigned char* src = saved + ((size_t)bh * nBlk + (cp >> 6)) * kSavedBytes;
-            tc::bulk_load(smem + OFF_TINV, src + SAVED_T * SLAB64, 2 * SLAB64, &sm.bar[6]);
+            const int c = lane & 7, which = lane >> 3;   // 0: T, 1: A_ak
+            tc::bulk_load(smem + (which == 0 ? OFF_TINV : OFF_AAK) + c * CB64, src + (size_t)(which == 0 ? SAVED_T : SAVED_AAK) * GTILE + c * GCB,
+                          64 * 16, &sm.bar[6]);
         }
     };
     bool loaded_next = false;
     for (int order = 0; order < n_runs; ++order) {
     const RunPlan run = run_at(unit_lo, unit_hi, SEG, order);
     bh = run.chain;
+    if (fast[bh] != 0) continue;
     bi = bh / H;
     L = min((int)length[bi], Tlen);
     seq_base = (size_t)bi * Tlen * tok_stride + (size_t)(bh % H) * kN;
@@ -603,7 +622,7 @@ wkv7_chunk_bwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     // from the residual (in L2 since the bulk copy) rather than from shared memory, whose bandwidth
                     // the running products need for their operands
                     const __nv_bfloat16* s0b = reinterpret_cast<const __nv_bfloat16*>(
-                                                   saved + ((size_t)bh * nBlk + (cur_p >> 6)) * kSavedBytes + SAVED_S0 * SLAB64 + (c >> 3) * CB64) + (c & 7);
+                                                   saved + ((size_t)bh * nBlk + (cur_p >> 6)) * kSavedBytes + SAVED_S0 * GTILE + (c >> 3) * GCB) + (c & 7);
                     __nv_bfloat16 sv[16];   // all loads in flight at once
 #pragma unroll
                     for (int rr = 0; rr < 16; ++rr) sv[rr] = __ldg(s0b + (rq * 16 + rr) * 8);
@@ -801,8 +820,8 @@ int* wkv7_chunk_status_word();
 
 int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const uint32_t* length, const uint8_t* ns, const void* dy,
-                   const void* ds_out, void* residual, const int* residual_mark, void* dw, void* dr, void* dk, void* dv,
-                   void* da, void* db, void* ds0) {
+                   const void* ds_out, void* residual, const int* residual_mark, const int* fast, void* dw, void* dr,
+                   void* dk, void* dv, void* da, void* db, void* ds0) {
     typedef __nv_bfloat16 bf;
     static DeviceOnce smem_attr;   // the opt-in to large dynamic shared memory is a per-device function attribute
     if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv7_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); }))
@@ -830,7 +849,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
         if (cudaMemsetAsync(carry_flag, 0, (size_t)kHandoffSlots * sizeof(int), st) != cudaSuccess) return B200WKV_ELAUNCH;
         int Tl = T, Hl = H, seg = plan.seg;
         void* args[] = {&Tl, &Hl, &pw, &pr, &pk, &pv, &pa, &pb, &length, &ns, &pdy, &pds, &ck, &sl, &gw, &gr, &gk, &gv, &ga,
-                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps, &saved, &residual_mark};
+                        &gb, &gs, &status, &BH, &seg, &carry, &carry_flag, &maps, &saved, &residual_mark, &fast};
         // cooperative launch: the runtime guarantees that all CTAs are resident at once, which the
         // carry hand-over relies on; if it refuses, fall through to one CTA per sequence
         if (cudaLaunchCooperativeKernel((const void*)wkv7_chunk_bwd_kernel, dim3(plan.grid), dim3(256), args, SMEM_BYTES, st) ==
@@ -840,7 +859,7 @@ int wkv7_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     }
     wkv7_chunk_bwd_kernel<<<plan.seg > 1 ? BH : plan.grid, 256, SMEM_BYTES, st>>>(T, H, pw, pr, pk, pv, pa, pb, length, ns, pdy, pds, ck,
                                                                                sl, gw, gr, gk, gv, ga, gb, gs, status, BH, 1,
-                                                                               carry, carry_flag, maps, saved, residual_mark);
+                                                                               carry, carry_flag, maps, saved, residual_mark, fast);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

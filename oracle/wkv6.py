@@ -95,7 +95,7 @@ def wkv6_bwd(r, k, v, w, u, s, length, new_starts, dy, ds_out, version="6"):
     dd = np.zeros((T, H, N, 1), dtype=r.dtype)
     du = np.zeros((H, N, 1), dtype=r.dtype)
     dS = np.zeros_like(S)
-    L = int(length)
+    L = min(int(length), T)      # `out_s <- S if t < length`: a length beyond T returns the last state
     for t in range(T - 1, -1, -1):
         if t == L - 1:
             dS = dS + ds_out

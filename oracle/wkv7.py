@@ -118,7 +118,7 @@ def wkv7_bwd(r, w, k, v, a, b, s, length, new_starts, dy, ds_out):
     dr = np.zeros_like(r); dw = np.zeros_like(r); dk = np.zeros_like(r)
     dv = np.zeros_like(r); da = np.zeros_like(r); db = np.zeros_like(r)
     dS = np.zeros_like(S)
-    L = int(length)
+    L = min(int(length), T)      # `out_s <- S if t < length`: a length beyond T returns the last state
     for t in range(T - 1, -1, -1):
         if t == L - 1:
             dS = dS + ds_out

@@ -89,7 +89,7 @@ def test_wkv7_reverse_loop_matches_autograd():
     ns = np.zeros(20, dtype=bool); ns[[7, 8, 15]] = True
     rng = np.random.default_rng(1)
     dy = rng.standard_normal((20, 2, 8)); ds = rng.standard_normal((2, 8, 8))
-    for length in (13, 20, 0, 8):
+    for length in (13, 20, 0, 8, 25):
         names = ["r", "w", "k", "v", "a", "b", "s0"]
         ts = [_t(d[n][0]) for n in names]
         s_out, y = torch_ref.wkv7_base_torch(*ts, length, torch.tensor(ns))
@@ -105,7 +105,7 @@ def test_wkv6_reverse_loop_matches_autograd(version):
     ns = np.zeros(18, dtype=bool); ns[[5, 6, 12]] = True
     rng = np.random.default_rng(2)
     dy = rng.standard_normal((18, 2, 8)); ds = rng.standard_normal((2, 8, 8))
-    for length in (11, 18, 0):
+    for length in (11, 18, 0, 23):
         r, k, v, s0 = [_t(d[n][0]) for n in ["r", "k", "v", "s0"]]
         w = _t(d["w"][0] if version == "6" else d["w"]); u = _t(d["u"])
         s_out, y = torch_ref.wkv6_base_torch(r, k, v, w, u, s0, length, torch.tensor(ns), version)
