@@ -109,12 +109,14 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
 
     issue(nBlk - 1);
     issue(nBlk - 2);
+    uint8_t flag_here = new_starts[(size_t)bi * Tlen + (size_t)(nBlk - 1) * kC];   // start flag of the block's first token
     for (int blk = nBlk - 1; blk >= 0; --blk) {
+        cp_async_wait<1>();                     // the copies of block blk have landed (one younger group may be in flight)
+        __syncthreads();                        // ... for every thread; and everyone is done with the stage refilled next
         issue(blk - 2);
-        cp_async_wait<2>();                     // the copies of block blk have landed (two younger groups may be in flight)
-        __syncthreads();
+        const uint8_t flag_next = (blk > 0) ? new_starts[(size_t)bi * Tlen + (size_t)(blk - 1) * kC] : 0;   // asked for a block ahead
         const CarryStage& s = stages[blk % kStages];
-        const int p = blk * kC, p1 = p + kC;
+        const int p1 = (blk + 1) * kC;
         // cotangent of the returned state enters behind token length - 1
         if (p1 == L && ds_out != nullptr) add_ds_out();
         // the gradient leaving this block, in bf16: to global memory for the gradient kernel, and as the left
@@ -163,13 +165,13 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
             }
         }
         // a start flag on the block's first token cuts the dependency on everything before it
-        if (new_starts[(size_t)bi * Tlen + p] != 0) {
+        if (flag_here != 0) {
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
         }
-        __syncthreads();                        // this stage may be refilled by the next iteration's copies
+        flag_here = flag_next;
     }
     if (L == 0 && ds_out != nullptr) add_ds_out();   // the returned state IS the input state
 #pragma unroll
