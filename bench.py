@@ -2,7 +2,7 @@
 H*N = 2048, T = 4096, bf16, batch-sharded over N GPUs with no collective on the path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
-    python bench.py --case {wkv7,wkv7-fwd,wkv6,decode,config2} [--batch B --seq T --heads H --iters I]
+    python bench.py --case {wkv7,wkv7-fwd,wkv6,decode,decode-packed,token-shift,config2} [--batch B --seq T --heads H --iters I]
     torchrun --nproc-per-node N bench.py --case fsdp      (the train-step configuration's collectives)
 
 One "step" is one forward (saving the backward's residual) plus one backward over one batch of
@@ -51,6 +51,10 @@ METRIC = "wkv7_fwd_bwd_tokens_per_s"
 # ncu captures summarised under profiles/, with the hash of the kernel sources they were taken from.
 # Traffic is proportional to B; the figure is dropped (null) when the sources no longer match.
 NCU_TRAFFIC = {"sources": "", "B": 8, "wkv7_fwd": None, "wkv7_bwd": None}
+# The backward call is timed as a whole (CUDA events around the call): its device time is the sequential
+# state-gradient carry followed by the block-parallel gradient kernel; the launch list under profiles/
+# gives each kernel's share.  Traffic of the backward is the sum over both kernels.
+KERNELS = {"wkv7_fwd": ["wkv7_chunk_fwd_kernel"], "wkv7_bwd": ["wkv7_carry_bwd_kernel", "wkv7_grad_bwd_kernel"]}
 
 
 def kernel_source_hash():
@@ -339,8 +343,34 @@ def bench_configs(torch, dev, world, rank, peak):
                       "us_per_layer_step": us_layer, "ms_per_token_32_layers": ms / steps,
                       "tokens_per_s_per_gpu": Bd * steps / (ms / 1e3), "algorithmic_bytes_per_layer_step": nb,
                       "roofline_frac": nb / (us_layer / 1e6) / 1e9 / peak, "launches": steps * L}
-    del state
+    del state, graph
     torch.cuda.empty_cache()
+    if world == 1:
+        # the same step at 1024 sequences (8 layers, 2.8 GB of state): a launch moves 708 MB instead of 177 MB, so the
+        # fixed cost of a launch (first loads in flight, last stores drained) weighs a quarter as much
+        Bw, Lw = 1024, 8
+        state = torch.zeros(Bw, Lw, 2 + N, D, dtype=torch.bfloat16, device=dev)
+        xw = make_wkv7_device_inputs(Bw, 1, Hd, N, torch.bfloat16, dev, 1240, grads=False)
+        aw = [xw[n] for n in ("r", "w", "k", "v", "a", "b")]
+
+        def wide():
+            for layer in range(Lw):
+                rwkv7.wkv7_step_packed(*aw, state, layer)
+        wide()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                wide()
+        torch.cuda.current_stream().wait_stream(side)
+        ms = cuda_ms(torch, graph.replay, 2, 20)
+        nbw = Bw * Hd * (2 * N * N + 7 * N) * 2
+        out["config5"]["at_1024_sequences"] = {"us_per_layer_step": 1e3 * ms / Lw, "algorithmic_bytes_per_layer_step": nbw,
+                                               "roofline_frac": nbw / (ms / Lw / 1e3) / 1e9 / peak}
+        del state, graph
+        torch.cuda.empty_cache()
     return out
 
 
@@ -414,6 +444,31 @@ def run_case(args):
                 leaf.grad = None
             s, y = rwkv6.CudaRWKV.inner_loop(*leaves, x["length"], x["new_starts"])
             torch.autograd.backward((y, s), (x["dy"], x["ds"]))
+    elif args.case == "decode-packed":   # config 5's step: one layer's block of the packed container, in place, 4 layers
+        x = make_wkv7_device_inputs(B, 1, Hn, N, torch.bfloat16, dev, 1, grads=False)
+        state = torch.zeros(B, 4, 2 + N, Hn * N, dtype=torch.bfloat16, device=dev)
+        state[:, :, 2:] = x["s0"].reshape(B, 1, N, Hn * N)
+        a = [x[n] for n in ("r", "w", "k", "v", "a", "b")]
+
+        def fn():
+            for layer in range(4):
+                rwkv7.wkv7_step_packed(*a, state, layer)
+    elif args.case == "token-shift":     # forward + backward of the six-way token shift over (B, T, H*N)
+        from jaxrwkv_b200.token_shift import token_shift
+        g = torch.Generator(device=dev).manual_seed(3)
+        D = Hn * N
+        xs = torch.randn(B, Tn, D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        prev = torch.randn(B, D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        mix = torch.rand(6, D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        length = torch.full((B,), Tn, dtype=torch.int32, device=dev)
+        starts = torch.zeros(B, Tn, dtype=torch.uint8, device=dev)
+        gout = torch.randn(6, B, Tn, D, device=dev, generator=g).to(torch.bfloat16)
+
+        def fn():
+            for leaf in (xs, prev, mix):
+                leaf.grad = None
+            mixed, new_prev = token_shift(xs, prev, mix, length, starts)
+            torch.autograd.backward((mixed,), (gout,))
     else:   # decode: chained single-token steps on a carried state
         x = make_wkv7_device_inputs(B, 1, Hn, N, torch.bfloat16, dev, 1, grads=False)
         st = [x["s0"]]
@@ -440,7 +495,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the configs / strong / sustained blocks")
-    ap.add_argument("--case", default=None, choices=["wkv7", "wkv7-fwd", "wkv6", "decode", "config2", "fsdp"])
+    ap.add_argument("--case", default=None, choices=["wkv7", "wkv7-fwd", "wkv6", "decode", "decode-packed", "token-shift", "config2", "fsdp"])
     ap.add_argument("--seq", type=int, default=T)
     ap.add_argument("--heads", type=int, default=H)
     ap.add_argument("--iters", type=int, default=2)
@@ -581,7 +636,7 @@ def main():
     achieved = dom_bytes / (dom_ms / 1e3) / 1e9
     src = kernel_source_hash()
     traffic = NCU_TRAFFIC[dom] * B / NCU_TRAFFIC["B"] if (NCU_TRAFFIC[dom] and NCU_TRAFFIC["sources"] == src) else None
-    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": which,
+    roofline = {"bound": "hbm", "kernel": dom, "kernels": KERNELS[dom], "achieved": achieved, "peak": peak, "peak_source": which,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                 "traffic_source": (f"ncu capture at B={NCU_TRAFFIC['B']} of kernel sources {NCU_TRAFFIC['sources']}, scaled by B"
                                    if traffic else f"none for kernel sources {src} (the committed capture is of {NCU_TRAFFIC['sources'] or 'no build'})"),
@@ -600,9 +655,13 @@ def main():
             "value_per_gpu": value / world, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu,
             "clocks": clocks, "sustained": sustained, "strong": strong, "configs": configs,
             "device_status": status,
-            # launches of this library's kernels per step and rank inside the device-timed region: the forward
-            # kernel and the backward kernel (plus one memset node clearing the backward's hand-over flags)
-            "gpu_launches": 2 * args.steps * world, "memset_nodes": args.steps * world}
+            # launches of this library's kernels per step and rank inside the device-timed region.  Forward call:
+            # the chunked kernel and the sequential kernel that redoes the call when a decay left the chunked
+            # kernel's range (it returns at once otherwise).  Backward call: state-gradient carry, gradient kernel,
+            # the one-kernel backward for sequences the forward did not mark as fast (none here: it returns at
+            # once) and the sequential backward under the same condition as the forward's; plus one memset node
+            # clearing the one-kernel backward's hand-over flags.
+            "gpu_launches": 6 * args.steps * world, "memset_nodes": args.steps * world}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -88,8 +88,8 @@ int b200wkv7_fwd(void* stream, int dtype, int B, int T, int H, int N,
  * src/jaxrwkv/rwkv7.py:175-180): rows 2.. of a layer are the (H, N, N) block of this operator
  * (rwkv7.py:255, :260), so under a batch the blocks of one layer are `state_batch_stride` elements
  * apart.  `state` points at the block of batch row 0; streams are (B, 1, H, N), y likewise.  No copy
- * of the state is made on either side of the step.  `state` must be 16-byte aligned and the stride
- * a multiple of 16 bytes (B200WKV_EUNSUPPORTED otherwise).  length == 0 leaves a row's state as it
+ * of the state is made on either side of the step.  `state` must be 32-byte aligned, the stride a
+ * multiple of 32 bytes and the six streams 16-byte aligned (B200WKV_EUNSUPPORTED otherwise).  length == 0 leaves a row's state as it
  * is; a start flag zeroes it before the token (as b200wkv7_fwd). */
 int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N,
                           const void* w, const void* r, const void* k, const void* v,

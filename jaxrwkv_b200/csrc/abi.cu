@@ -239,7 +239,10 @@ int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N, const vo
     if (!w || !r || !k || !v || !a || !b || !state || !length || !new_starts || !y) return B200WKV_ENULL;
     const long long esz = dtype == B200WKV_F32 ? 4 : 2;
     if (state_batch_stride < (long long)H * N * N) return B200WKV_ESHAPE;
-    if ((reinterpret_cast<uintptr_t>(state) & 15u) != 0 || (state_batch_stride * esz) % 16 != 0) return B200WKV_EUNSUPPORTED;
+    const uintptr_t vec_bits = reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(r) | reinterpret_cast<uintptr_t>(k) |
+                               reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
+    if ((reinterpret_cast<uintptr_t>(state) & 31u) != 0 || (state_batch_stride * esz) % 32 != 0 || (vec_bits & 15u) != 0)
+        return B200WKV_EUNSUPPORTED;
     return wkv7_step_stream((cudaStream_t)stream, dtype, B, H, w, r, k, v, a, b, state, length, new_starts, y, state,
                             state_batch_stride);
 }

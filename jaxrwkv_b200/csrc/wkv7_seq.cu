@@ -541,8 +541,12 @@ int wkv7_step_stream(cudaStream_t st, int dtype, int B, int H, const void* w, co
 int wkv7_step(cudaStream_t st, int dtype, int B, int H, const void* w, const void* r, const void* k, const void* v,
               const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
               void* s_out) {
-    // states on 16-byte boundaries (every framework allocation is) take the pipelined stream kernel
-    if (((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s_out)) & 15u) == 0)
+    // operands on 16-byte and the result state on 32-byte boundaries (every framework allocation is) take the
+    // pipelined stream kernel
+    const uintptr_t in_bits = reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(r) |
+                              reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(a) |
+                              reinterpret_cast<uintptr_t>(b);
+    if ((in_bits & 15u) == 0 && (reinterpret_cast<uintptr_t>(s_out) & 31u) == 0)
         return wkv7_step_stream(st, dtype, B, H, w, r, k, v, a, b, s0, length, ns, y, s_out, (long long)H * kN * kN);
     if (dtype == B200WKV_F32)
         wkv7_step_kernel<float><<<B * H, 256, 0, st>>>(H, (const float*)w, (const float*)r, (const float*)k, (const float*)v,
