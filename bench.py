@@ -2,7 +2,7 @@
 H*N = 2048, T = 4096, bf16, batch-sharded over N GPUs with no collective on the path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
-    python bench.py --case {wkv7,wkv7-fwd,wkv6,decode,decode-packed,token-shift,config2} [--batch B --seq T --heads H --iters I]
+    python bench.py --case {wkv7,wkv7-fwd,wkv6,decode,decode-packed,token-shift,mix,config2} [--batch B --seq T --heads H --iters I]
     torchrun --nproc-per-node N bench.py --case fsdp      (the train-step configuration's collectives)
 
 One "step" is one forward (saving the backward's residual) plus one backward over one batch of
@@ -418,6 +418,57 @@ def run_fsdp_case(args):
     dist.destroy_process_group()
 
 
+def run_mix_case(torch, dev, B, Tn, Hn, iters):
+    """Times b200wkv7_mix_{pre,post}_{fwd,bwd} through the C ABI on (B*T, H*64) bf16 streams and prints, per kernel,
+    the time and the algorithmic GB/s (streams read + streams written, 2 bytes per element)."""
+    from jaxrwkv_b200 import _lib
+    lib = _lib.load()
+    C, rows = Hn * N, B * Tn
+    g = torch.Generator(device=dev).manual_seed(5)
+    stream = lambda: torch.randn(rows, C, device=dev, generator=g).to(torch.bfloat16)
+    param = lambda: torch.rand(C, device=dev, generator=g).add_(0.5).to(torch.bfloat16)
+    ins = [stream() for _ in range(6)]          # k, wl, al, v, v_first, vl  /  y, r, k, v, g, (gx)
+    grads = [stream() for _ in range(5)]
+    outs = [torch.empty(rows, C, dtype=torch.bfloat16, device=dev) for _ in range(6)]
+    pars = [param() for _ in range(5)]
+    n_part = lib.b200wkv7_mix_partial_rows(rows, Hn, N)
+    partial = torch.empty(n_part, 5, C, dtype=torch.float32, device=dev)
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    p = lambda ts: [t.data_ptr() for t in ts]
+    calls = {
+        "mix_pre_fwd": (11, lambda: lib.b200wkv7_mix_pre_fwd(st(), _lib.BF16, rows, Hn, N, 1, *p(ins), *p(pars), *p(outs[:5]))),
+        "mix_pre_bwd": (17, lambda: lib.b200wkv7_mix_pre_bwd(st(), _lib.BF16, rows, Hn, N, 1, *p(ins), *p(pars), *p(grads), *p(outs),
+                                                             partial.data_ptr())),
+        "mix_post_fwd": (6, lambda: lib.b200wkv7_mix_post_fwd(st(), _lib.BF16, rows, Hn, N, 64e-5, *p(ins[:5]), *p(pars[:3]), outs[0].data_ptr())),
+        "mix_post_bwd": (11, lambda: lib.b200wkv7_mix_post_bwd(st(), _lib.BF16, rows, Hn, N, 64e-5, *p(ins[:5]), *p(pars[:3]), ins[5].data_ptr(),
+                                                               *p(outs[:5]), partial.data_ptr())),
+    }
+    for name, (n_streams, fn) in calls.items():
+        assert fn() == 0, name
+        ms = cuda_ms(torch, fn, 2, iters)
+        nbytes = n_streams * rows * C * 2
+        print(f"case mix {name} rows={rows} C={C}: {ms * 1e3:.1f} us, {n_streams} streams, {nbytes / ms / 1e6:.0f} GB/s algorithmic")
+    # the same forward arithmetic as one framework op after another (what runs without these kernels when nothing fuses)
+    k, wl, al, v, vf, vl = ins
+    w0, a0, v0, k_k, k_a = pars
+
+    def eager_pre():
+        w = -torch.nn.functional.softplus(-(w0 + wl)) - 0.5
+        vp = v + (vf - v) * torch.sigmoid(v0 + vl)
+        a = torch.sigmoid(a0 + al)
+        kk = (k * k_k).view(rows, Hn, N)
+        kk = (kk / torch.clamp(torch.linalg.norm(kk, dim=-1, keepdim=True), min=1e-12)).view(rows, C)
+        return w, k * (1 + (a - 1) * k_a), vp, -kk, kk * a
+
+    def eager_post():
+        y, r, kp, vp, g_ = ins[:5]
+        x = torch.nn.functional.group_norm(y, Hn, pars[0], pars[1], 64e-5)
+        bonus = (r.view(rows, Hn, N) * kp.view(rows, Hn, N) * pars[2].view(Hn, N)).sum(-1, keepdim=True)
+        return (x + (bonus * vp.view(rows, Hn, N)).view(rows, C)) * g_
+    for name, fn in (("eager torch, before the operator (forward)", eager_pre), ("eager torch, after the operator (forward)", eager_post)):
+        print(f"case mix {name}: {cuda_ms(torch, fn, 2, iters) * 1e3:.1f} us")
+
+
 def run_case(args):
     """One small workload a few times, its last iteration timed: for profilers and quick checks."""
     if args.case == "fsdp":
@@ -469,6 +520,8 @@ def run_case(args):
                 leaf.grad = None
             mixed, new_prev = token_shift(xs, prev, mix, length, starts)
             torch.autograd.backward((mixed,), (gout,))
+    elif args.case == "mix":             # the elementwise stages on both sides of the operator, forward and backward
+        return run_mix_case(torch, dev, B, Tn, Hn, args.iters)
     else:   # decode: chained single-token steps on a carried state
         x = make_wkv7_device_inputs(B, 1, Hn, N, torch.bfloat16, dev, 1, grads=False)
         st = [x["s0"]]
@@ -495,7 +548,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the configs / strong / sustained blocks")
-    ap.add_argument("--case", default=None, choices=["wkv7", "wkv7-fwd", "wkv6", "decode", "decode-packed", "token-shift", "config2", "fsdp"])
+    ap.add_argument("--case", default=None, choices=["wkv7", "wkv7-fwd", "wkv6", "decode", "decode-packed", "token-shift", "mix", "config2", "fsdp"])
     ap.add_argument("--seq", type=int, default=T)
     ap.add_argument("--heads", type=int, default=H)
     ap.add_argument("--iters", type=int, default=2)

@@ -178,6 +178,46 @@ int b200wkv_token_shift_bwd(void* stream, int dtype, int B, int T, int D, int M,
                             const void* gout, const void* gstate,
                             void* gx, void* gprev, void* gmix);
 
+/* ------------------------------------------- around the operator: time mixing ----
+ * The elementwise work jaxrwkv's time mixing does on either side of the recurrence
+ * (src/jaxrwkv/rwkv7.py:238-252 and :263-265), each side in one pass.  Streams are (rows, H*N) with
+ * rows = B*T and N == 64 (H <= 128); per-channel parameters are (H*N,); all of one element type; every
+ * pointer 16-byte aligned (B200WKV_EUNSUPPORTED otherwise).
+ *
+ * before the operator:   w   = -softplus(-(w0 + wl)) - 0.5          wl = output of the decay LoRA (:238)
+ *                        a   = sigmoid(a0 + al)                     al = output of the a LoRA (:245)
+ *                        v'  = v + (v_first - v) * sigmoid(v0 + vl) when use_vmix (layers > 0, :243), else v
+ *                        kk  = (k * k_k) / max(||k * k_k||_head, 1e-12)   (:248-251)
+ *                        k'  = k * (1 + (a - 1) * k_a)              (:252)
+ *                        a_i = -kk,  b_i = kk * a                   (:257)
+ *   outputs w, k_out = k', v_out = v', a_i, b_i are the operator's operands (with r unchanged).
+ * after the operator:    x = (group_norm(y; H groups, eps) * ln_w + ln_b + (sum_n r k' r_k) * v') * g   (:263-265)
+ *
+ * The backward calls take the forward's inputs again (nothing is saved) and the cotangents of the
+ * outputs; parameter gradients come back as fp32 partial sums, `partial` =
+ * (b200wkv7_mix_partial_rows(rows, H, N), P, H*N) with P = 5 (dw0, da0, dv0, dk_k, dk_a) before and
+ * P = 3 (d ln_w, d ln_b, d r_k) after the operator; the caller adds over the first axis (deterministic,
+ * no atomics).  With use_vmix == 0, v_first / vl / v0 and their gradients may be NULL. */
+int b200wkv7_mix_partial_rows(long long rows, int H, int N);
+int b200wkv7_mix_pre_fwd(void* stream, int dtype, long long rows, int H, int N, int use_vmix,
+                         const void* k, const void* wl, const void* al, const void* v,
+                         const void* v_first, const void* vl,
+                         const void* w0, const void* a0, const void* v0, const void* k_k, const void* k_a,
+                         void* w, void* k_out, void* v_out, void* a_i, void* b_i);
+int b200wkv7_mix_pre_bwd(void* stream, int dtype, long long rows, int H, int N, int use_vmix,
+                         const void* k, const void* wl, const void* al, const void* v,
+                         const void* v_first, const void* vl,
+                         const void* w0, const void* a0, const void* v0, const void* k_k, const void* k_a,
+                         const void* gw, const void* gk_out, const void* gv_out, const void* ga_i, const void* gb_i,
+                         void* dk, void* dwl, void* dal, void* dv, void* dv_first, void* dvl, float* partial);
+int b200wkv7_mix_post_fwd(void* stream, int dtype, long long rows, int H, int N, float eps,
+                          const void* y, const void* r, const void* k, const void* v, const void* g,
+                          const void* ln_w, const void* ln_b, const void* r_k, void* x);
+int b200wkv7_mix_post_bwd(void* stream, int dtype, long long rows, int H, int N, float eps,
+                          const void* y, const void* r, const void* k, const void* v, const void* g,
+                          const void* ln_w, const void* ln_b, const void* r_k, const void* gx,
+                          void* dy, void* dr, void* dk, void* dv, void* dg, float* partial);
+
 /* Forward + backward in one call with NO residual buffer from the caller (no counterpart in
  * jaxrwkv: its kernels always take the residuals as operands).
  *

@@ -32,6 +32,11 @@ PROTOTYPES = {
     "b200wkv4_bwd": (_I, [_P, _I, _I, _I, _I] + [_P] * 9 + [_P, _SZ] + [_P] * 5 + [_U]),
     "b200wkv_token_shift_fwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 7),
     "b200wkv_token_shift_bwd": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 10),
+    "b200wkv7_mix_partial_rows": (_I, [ctypes.c_longlong, _I, _I]),
+    "b200wkv7_mix_pre_fwd": (_I, [_P, _I, ctypes.c_longlong, _I, _I, _I] + [_P] * 16),
+    "b200wkv7_mix_pre_bwd": (_I, [_P, _I, ctypes.c_longlong, _I, _I, _I] + [_P] * 23),
+    "b200wkv7_mix_post_fwd": (_I, [_P, _I, ctypes.c_longlong, _I, _I, ctypes.c_float] + [_P] * 9),
+    "b200wkv7_mix_post_bwd": (_I, [_P, _I, ctypes.c_longlong, _I, _I, ctypes.c_float] + [_P] * 15),
     "b200wkv7_static_scratch_bytes": (_SZ, []),
     "b200wkv7_fwd_bwd_static": (_I, [_P, _I, _I, _I, _I, _I] + [_P] * 9 + [_P, _P] + [_P, _P] + [_P] * 7 + [_U]),
 }

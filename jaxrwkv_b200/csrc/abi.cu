@@ -1,4 +1,5 @@
 // extern "C" entry points declared in include/b200wkv.h: argument validation and dispatch.
+#include <initializer_list>
 #include "common.cuh"
 #include "chunk_common.cuh"
 #include "../../include/b200wkv_debug.h"
@@ -50,6 +51,19 @@ int wkv4_bwd(cudaStream_t st, int dtype, int B, int T, int C, const void* w, con
              const void* gy, const uint32_t* length, const uint8_t* ns, const void* gs_new, const void* residual,
              void* gw, void* gu, void* gk, void* gv, void* gs);
 
+int wkv7_mix_partial_rows(int rows, int C);
+int wkv7_mix_pre_fwd(cudaStream_t st, int dtype, int rows, int C, int use_vmix, const void* k, const void* wl, const void* al,
+                     const void* v, const void* vf, const void* vl, const void* w0, const void* a0, const void* v0,
+                     const void* k_k, const void* k_a, void* w, void* kp, void* vp, void* ai, void* bi);
+int wkv7_mix_pre_bwd(cudaStream_t st, int dtype, int rows, int C, int use_vmix, const void* k, const void* wl, const void* al,
+                     const void* v, const void* vf, const void* vl, const void* w0, const void* a0, const void* v0,
+                     const void* k_k, const void* k_a, const void* gw, const void* gkp, const void* gvp, const void* gai,
+                     const void* gbi, void* dk, void* dwl, void* dal, void* dv, void* dvf, void* dvl, float* partial);
+int wkv7_mix_post_fwd(cudaStream_t st, int dtype, int rows, int C, float eps, const void* y, const void* r, const void* kp,
+                      const void* vp, const void* g, const void* ln_w, const void* ln_b, const void* r_k, void* x);
+int wkv7_mix_post_bwd(cudaStream_t st, int dtype, int rows, int C, float eps, const void* y, const void* r, const void* kp,
+                      const void* vp, const void* g, const void* ln_w, const void* ln_b, const void* r_k, const void* gx, void* dy,
+                      void* dr, void* dkp, void* dvp, void* dg, float* partial);
 int token_shift_fwd(cudaStream_t st, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
                     const void* mix, const uint32_t* length, const uint8_t* ns, void* out, void* state_out);
 int token_shift_bwd(cudaStream_t st, int dtype, int B, int T, int D, int M, const void* x, const void* prev,
@@ -245,6 +259,77 @@ int b200wkv7_step_inplace(void* stream, int dtype, int B, int H, int N, const vo
         return B200WKV_EUNSUPPORTED;
     return wkv7_step_stream((cudaStream_t)stream, dtype, B, H, w, r, k, v, a, b, state, length, new_starts, y, state,
                             state_batch_stride);
+}
+
+namespace {
+int check_mix(int dtype, long long rows, int H, int N) {
+    if (dtype != B200WKV_F32 && dtype != B200WKV_BF16) return B200WKV_EDTYPE;
+    if (N != kN || H < 1 || H > 128 || rows < 1 || rows > 2147483647LL) return B200WKV_ESHAPE;
+    return B200WKV_OK;
+}
+bool aligned16(std::initializer_list<const void*> ps) {
+    for (const void* p : ps)
+        if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return false;
+    return true;
+}
+}  // namespace
+
+int b200wkv7_mix_partial_rows(long long rows, int H, int N) {
+    if (check_mix(B200WKV_F32, rows, H, N) != B200WKV_OK) return 0;
+    return wkv7_mix_partial_rows((int)rows, H * N);
+}
+
+int b200wkv7_mix_pre_fwd(void* stream, int dtype, long long rows, int H, int N, int use_vmix, const void* k, const void* wl,
+                         const void* al, const void* v, const void* v_first, const void* vl, const void* w0, const void* a0,
+                         const void* v0, const void* k_k, const void* k_a, void* w, void* k_out, void* v_out, void* a_i,
+                         void* b_i) {
+    int st = check_mix(dtype, rows, H, N);
+    if (st != B200WKV_OK) return st;
+    if (!k || !wl || !al || !v || !w0 || !a0 || !k_k || !k_a || !w || !k_out || !v_out || !a_i || !b_i) return B200WKV_ENULL;
+    if (use_vmix && (!v_first || !vl || !v0)) return B200WKV_ENULL;
+    if (!aligned16({k, wl, al, v, v_first, vl, w0, a0, v0, k_k, k_a, w, k_out, v_out, a_i, b_i})) return B200WKV_EUNSUPPORTED;
+    return wkv7_mix_pre_fwd((cudaStream_t)stream, dtype, (int)rows, H * N, use_vmix ? 1 : 0, k, wl, al, v, v_first, vl, w0, a0,
+                            v0, k_k, k_a, w, k_out, v_out, a_i, b_i);
+}
+
+int b200wkv7_mix_pre_bwd(void* stream, int dtype, long long rows, int H, int N, int use_vmix, const void* k, const void* wl,
+                         const void* al, const void* v, const void* v_first, const void* vl, const void* w0, const void* a0,
+                         const void* v0, const void* k_k, const void* k_a, const void* gw, const void* gk_out,
+                         const void* gv_out, const void* ga_i, const void* gb_i, void* dk, void* dwl, void* dal, void* dv,
+                         void* dv_first, void* dvl, float* partial) {
+    int st = check_mix(dtype, rows, H, N);
+    if (st != B200WKV_OK) return st;
+    if (!k || !wl || !al || !v || !w0 || !a0 || !k_k || !k_a || !gw || !gk_out || !gv_out || !ga_i || !gb_i || !dk || !dwl ||
+        !dal || !dv || !partial)
+        return B200WKV_ENULL;
+    if (use_vmix && (!v_first || !vl || !v0 || !dv_first || !dvl)) return B200WKV_ENULL;
+    if (!aligned16({k, wl, al, v, v_first, vl, w0, a0, v0, k_k, k_a, gw, gk_out, gv_out, ga_i, gb_i, dk, dwl, dal, dv, dv_first,
+                    dvl, partial}))
+        return B200WKV_EUNSUPPORTED;
+    return wkv7_mix_pre_bwd((cudaStream_t)stream, dtype, (int)rows, H * N, use_vmix ? 1 : 0, k, wl, al, v, v_first, vl, w0, a0,
+                            v0, k_k, k_a, gw, gk_out, gv_out, ga_i, gb_i, dk, dwl, dal, dv, dv_first, dvl, partial);
+}
+
+int b200wkv7_mix_post_fwd(void* stream, int dtype, long long rows, int H, int N, float eps, const void* y, const void* r,
+                          const void* k, const void* v, const void* g, const void* ln_w, const void* ln_b, const void* r_k,
+                          void* x) {
+    int st = check_mix(dtype, rows, H, N);
+    if (st != B200WKV_OK) return st;
+    if (!y || !r || !k || !v || !g || !ln_w || !ln_b || !r_k || !x) return B200WKV_ENULL;
+    if (!aligned16({y, r, k, v, g, ln_w, ln_b, r_k, x})) return B200WKV_EUNSUPPORTED;
+    return wkv7_mix_post_fwd((cudaStream_t)stream, dtype, (int)rows, H * N, eps, y, r, k, v, g, ln_w, ln_b, r_k, x);
+}
+
+int b200wkv7_mix_post_bwd(void* stream, int dtype, long long rows, int H, int N, float eps, const void* y, const void* r,
+                          const void* k, const void* v, const void* g, const void* ln_w, const void* ln_b, const void* r_k,
+                          const void* gx, void* dy, void* dr, void* dk, void* dv, void* dg, float* partial) {
+    int st = check_mix(dtype, rows, H, N);
+    if (st != B200WKV_OK) return st;
+    if (!y || !r || !k || !v || !g || !ln_w || !ln_b || !r_k || !gx || !dy || !dr || !dk || !dv || !dg || !partial)
+        return B200WKV_ENULL;
+    if (!aligned16({y, r, k, v, g, ln_w, ln_b, r_k, gx, dy, dr, dk, dv, dg, partial})) return B200WKV_EUNSUPPORTED;
+    return wkv7_mix_post_bwd((cudaStream_t)stream, dtype, (int)rows, H * N, eps, y, r, k, v, g, ln_w, ln_b, r_k, gx, dy, dr, dk,
+                             dv, dg, partial);
 }
 
 int b200wkv_debug_split_plan(int chains, int n_blk, int per_sm, int* grid, int* seg) {

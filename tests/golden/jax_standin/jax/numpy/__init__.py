@@ -69,3 +69,9 @@ def asarray(x, dtype=None):
 
 
 array = asarray
+
+
+class linalg:
+    @staticmethod
+    def norm(x, axis=None, keepdims=False):
+        return _wrap(_np.linalg.norm(_np.asarray(x), axis=axis, keepdims=keepdims))

@@ -115,6 +115,62 @@ def run_shift(mod, name, seed):
     print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
+def time_mixing_params(rng, C, H, lora=8):
+    """Random parameters of one RWKV-7 attention block with the reference's names and shapes (rwkv7.py:222-266)."""
+    u = lambda *shape, lo=-1.0, hi=1.0: rng.uniform(lo, hi, shape).astype(np.float32)
+    sq = lambda: {"weight": (u(C, C) / np.sqrt(C)).astype(np.float32)}
+    att = {n: u(1, 1, C, lo=0.0, hi=1.0) for n in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g")}
+    att.update(receptance=sq(), key=sq(), value=sq(), output=sq())
+    att.update(w0=u(1, 1, C, lo=-2.0, hi=1.0), w1=u(C, lora) / np.sqrt(C), w2=u(lora, C),
+               a0=u(1, 1, C), a1=u(C, lora) / np.sqrt(C), a2=u(lora, C),
+               v0=u(1, 1, C), v1=u(C, lora) / np.sqrt(C), v2=u(lora, C),
+               g1=u(C, lora) / np.sqrt(C), g2=u(lora, C),
+               k_k=u(1, 1, C, lo=0.5, hi=1.5), k_a=u(1, 1, C, lo=0.5, hi=1.5), r_k=u(H, C // H),
+               ln_x={"weight": u(C, lo=0.5, hi=1.5), "bias": u(C)})
+    return att
+
+
+def flatten_params(att, prefix="p_"):
+    out = {}
+    for k, v in att.items():
+        if isinstance(v, dict):
+            out.update({f"{prefix}{k}.{kk}": vv for kk, vv in v.items()})
+        else:
+            out[prefix + k] = v
+    return out
+
+
+def run_time_mixing(mod, name, seed):
+    """The whole time-mixing function of RWKV-7 (rwkv7.py:222-266) on random parameters, per sequence, for the first
+    layer (the value stream passes through) and a later one (mixed with ``v_first``), in float64."""
+    import jax.numpy as jnp
+    rng = np.random.default_rng(seed)
+    B, T, H, S = 3, 21, 2, 64
+    C = H * S
+    att = time_mixing_params(rng, C, H)
+    x = rng.standard_normal((B, T, C)).astype(np.float32)
+    state = (0.3 * rng.standard_normal((B, 1 + S, C))).astype(np.float32)
+    v_first = rng.standard_normal((B, T, C)).astype(np.float32)
+    ns = np.zeros((B, T), bool)
+    ns[0, [0, 9]] = True; ns[1, [4, 5, 20]] = True
+    length = np.asarray([21, 13, 21], dtype=np.uint32)
+    to64 = lambda t: ({k: to64(v) for k, v in t.items()} if isinstance(t, dict) else jnp.asarray(np.asarray(t, np.float64)))
+    att64 = to64(att)
+    arrays = dict(in_x=x, in_state=state, in_v_first=v_first, in_new_starts=ns, in_length=length, H=np.int64(H), S=np.int64(S))
+    arrays.update(flatten_params(att))
+    for layer_id in (0, 1):
+        outs, states, vfs = [], [], []
+        for i in range(B):
+            o, st, vf = mod.BaseRWKV.time_mixing_seq(to64(x[i]), to64(state[i]), to64(v_first[i]), att64, int(length[i]),
+                                                     jnp.asarray(ns[i]), H, S, layer_id)
+            outs.append(np.asarray(o)); states.append(np.asarray(st)); vfs.append(np.asarray(vf))
+        arrays.update({f"out_l{layer_id}": np.stack(outs), f"state_l{layer_id}": np.stack(states),
+                       f"v_first_l{layer_id}": np.stack(vfs)})
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **arrays)
+    print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def save(name, d, res):
     base_s, base_y = res["BaseRWKV"]
     scan_s, scan_y = res["ScanRWKV"]
@@ -157,6 +213,7 @@ def main():
     save("v7_small", d, run_v7(mods["7"], d))
 
     run_shift(mods["7"], "v7_token_shift", 104)
+    run_time_mixing(mods["7"], "v7_time_mixing", 105)
 
     # RWKV-6 / 5.2 / 5 -------------------------------------------------------------------
     for version, seed in (("6", 201), ("5_2", 202), ("5", 203)):

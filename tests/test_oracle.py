@@ -138,3 +138,36 @@ def test_token_shift_matches_reference_fixture(golden):
                                      g["in_mix"].astype(np.float64), int(g["in_length"][i]), g["in_new_starts"][i])
         assert rel_err(mixed[0], g["xk"][i]) < 1e-12
         np.testing.assert_array_equal(last, g["last"][i])
+
+
+def unflatten_params(g, prefix="p_"):
+    """The parameter dict of tests/golden/make_golden.flatten_params, rebuilt (float64)."""
+    att = {}
+    for key, val in g.items():
+        if not key.startswith(prefix):
+            continue
+        name = key[len(prefix):]
+        val = np.asarray(val, dtype=np.float64)
+        if "." in name:
+            outer, inner = name.split(".")
+            att.setdefault(outer, {})[inner] = val
+        else:
+            att[name] = val
+    return att
+
+
+@pytest.mark.parametrize("layer_id", [0, 1])
+def test_time_mixing_matches_reference_fixture(golden, layer_id):
+    """Fixture made by the reference's own time_mixing_seq (make_golden.run_time_mixing): the token shift, the
+    elementwise stages on both sides of the operator and the operator, composed as rwkv7.py:222-266 composes them."""
+    from oracle import time_mixing as tm
+    g = golden("v7_time_mixing")
+    att = unflatten_params(g)
+    H, S = int(g["H"]), int(g["S"])
+    for i in range(g["in_x"].shape[0]):
+        out, state, vf = tm.time_mixing_seq(g["in_x"][i].astype(np.float64), g["in_state"][i].astype(np.float64),
+                                            g["in_v_first"][i].astype(np.float64), att, int(g["in_length"][i]),
+                                            g["in_new_starts"][i], H, S, layer_id)
+        assert rel_err(out, g[f"out_l{layer_id}"][i]) < 1e-11
+        assert rel_err(state, g[f"state_l{layer_id}"][i]) < 1e-11
+        assert rel_err(vf, g[f"v_first_l{layer_id}"][i]) < 1e-12
