@@ -45,6 +45,36 @@ __device__ __forceinline__ void storev(__nv_bfloat16* p, const Vec<8>& v) {
     for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v.f[2 * i], v.f[2 * i + 1]);
     *reinterpret_cast<uint4*>(p) = raw;
 }
+// V channels as they lie in memory (16 or 8 bytes): what a thread keeps of a load until it uses it
+template <int V, typename T> struct RawVec;
+template <> struct RawVec<4, float> {
+    float4 q;
+    __device__ __forceinline__ void load(const float* p) { q = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ Vec<4> get() const { return Vec<4>{{q.x, q.y, q.z, q.w}}; }
+};
+template <> struct RawVec<4, __nv_bfloat16> {
+    uint2 q;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { q = *reinterpret_cast<const uint2*>(p); }
+    __device__ __forceinline__ Vec<4> get() const {
+        return Vec<4>{{__uint_as_float(q.x << 16), __uint_as_float(q.x & 0xffff0000u), __uint_as_float(q.y << 16),
+                       __uint_as_float(q.y & 0xffff0000u)}};
+    }
+};
+template <> struct RawVec<8, __nv_bfloat16> {
+    uint4 q;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { q = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ Vec<8> get() const {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        Vec<8> r;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            r.f[2 * i] = __uint_as_float(w[i] << 16);
+            r.f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+        return r;
+    }
+};
+
 template <int V> __device__ __forceinline__ Vec<V> zerov() {
     Vec<V> r;
 #pragma unroll
@@ -102,10 +132,11 @@ token_shift_bwd_kernel(int B, int Tlen, int D, const T* __restrict__ x, const T*
     const int t0 = tile * B200WKV_SHIFT_TILE;
     const int t1 = min(Tlen, t0 + B200WKV_SHIFT_TILE);
     const int last = last_row(length[bi], Tlen);
-    Vec<V> c[MM], acc[MM];
+    RawVec<V, T> craw[MM];   // the mix coefficients stay packed; unpacking them at each use is cheaper than the registers
+    Vec<V> acc[MM];
 #pragma unroll
     for (int m = 0; m < MM; ++m) {
-        c[m] = loadv<V>(mix + (size_t)m * D + d);
+        craw[m].load(mix + (size_t)m * D + d);
         acc[m] = zerov<V>();
     }
     const size_t base = (size_t)bi * Tlen * D + d;
@@ -116,40 +147,59 @@ token_shift_bwd_kernel(int B, int Tlen, int D, const T* __restrict__ x, const T*
 #pragma unroll
         for (int m = 0; m < MM; ++m) {
             const Vec<V> g = loadv<V>(gout + m * mstride + base + (size_t)t1 * D);
+            const Vec<V> cm = craw[m].get();
 #pragma unroll
-            for (int i = 0; i < V; ++i) carry.f[i] = fmaf(g.f[i], c[m].f[i], carry.f[i]);
+            for (int i = 0; i < V; ++i) carry.f[i] = fmaf(g.f[i], cm.f[i], carry.f[i]);
         }
     }
     Vec<V> xc = loadv<V>(x + base + (size_t)(t1 - 1) * D);
-#pragma unroll 2
-    for (int t = t1 - 1; t >= t0; --t) {
-        const bool st = ns[t] != 0;
-        // the row before: needed as this token's shift and as the next iteration's x
-        const Vec<V> xp = t > 0 ? loadv<V>(x + base + (size_t)(t - 1) * D) : loadv<V>(prev + (size_t)bi * D + d);
-        Vec<V> keep = zerov<V>(), pass = zerov<V>(), df;
+    // Tokens are taken four at a time: the 4 x (MM + 1) loads of a group are all issued, in packed form, before
+    // the first token of the group is worked on, so a thread has ~450 bytes in flight at 255 registers.
+    constexpr int G = 4;
+    for (int tg = t1 - 1; tg >= t0; tg -= G) {
+        RawVec<V, T> rg[G][MM], rx[G];
 #pragma unroll
-        for (int i = 0; i < V; ++i) df.f[i] = (st ? 0.f : xp.f[i]) - xc.f[i];
+        for (int j = 0; j < G; ++j) {
+            const int t = tg - j;
+            if (t >= t0) {
 #pragma unroll
-        for (int m = 0; m < MM; ++m) {
-            const Vec<V> g = loadv<V>(gout + m * mstride + base + (size_t)t * D);
-#pragma unroll
-            for (int i = 0; i < V; ++i) {
-                keep.f[i] = fmaf(g.f[i], 1.f - c[m].f[i], keep.f[i]);
-                pass.f[i] = fmaf(g.f[i], c[m].f[i], pass.f[i]);
-                acc[m].f[i] = fmaf(g.f[i], df.f[i], acc[m].f[i]);
+                for (int m = 0; m < MM; ++m) rg[j][m].load(gout + m * mstride + base + (size_t)t * D);
+                // the row before: needed as this token's shift and as the next token's x
+                rx[j].load(t > 0 ? x + base + (size_t)(t - 1) * D : prev + (size_t)bi * D + d);
             }
         }
 #pragma unroll
-        for (int i = 0; i < V; ++i) keep.f[i] += carry.f[i];
-        if (t == last && gstate != nullptr) {
-            const Vec<V> gs = loadv<V>(gstate + (size_t)bi * D + d);
+        for (int j = 0; j < G; ++j) {
+            const int t = tg - j;
+            if (t < t0) break;
+            const bool st = ns[t] != 0;
+            const Vec<V> xp = rx[j].get();
+            Vec<V> keep = zerov<V>(), pass = zerov<V>(), df;
 #pragma unroll
-            for (int i = 0; i < V; ++i) keep.f[i] += gs.f[i];
+            for (int i = 0; i < V; ++i) df.f[i] = (st ? 0.f : xp.f[i]) - xc.f[i];
+#pragma unroll
+            for (int m = 0; m < MM; ++m) {
+                const Vec<V> g = rg[j][m].get();
+                const Vec<V> cm = craw[m].get();
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    keep.f[i] = fmaf(g.f[i], 1.f - cm.f[i], keep.f[i]);
+                    pass.f[i] = fmaf(g.f[i], cm.f[i], pass.f[i]);
+                    acc[m].f[i] = fmaf(g.f[i], df.f[i], acc[m].f[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < V; ++i) keep.f[i] += carry.f[i];
+            if (t == last && gstate != nullptr) {
+                const Vec<V> gs = loadv<V>(gstate + (size_t)bi * D + d);
+#pragma unroll
+                for (int i = 0; i < V; ++i) keep.f[i] += gs.f[i];
+            }
+            storev(gx + base + (size_t)t * D, keep);
+#pragma unroll
+            for (int i = 0; i < V; ++i) carry.f[i] = st ? 0.f : pass.f[i];
+            xc = xp;
         }
-        storev(gx + base + (size_t)t * D, keep);
-#pragma unroll
-        for (int i = 0; i < V; ++i) carry.f[i] = st ? 0.f : pass.f[i];
-        xc = xp;
     }
     if (tile == 0) storev(gprev + (size_t)bi * D + d, carry);
 #pragma unroll
