@@ -39,11 +39,19 @@ int wkv7_chunk_status();
 size_t wkv6_seq_residual_bytes(int B, int T, int H);
 int wkv6_seq_fwd(cudaStream_t st, int dtype, int B, int T, int H, const void* r, const void* k, const void* v,
                  const void* w, int per_token, const void* u, const void* s0, const uint32_t* length,
-                 const uint8_t* ns, void* y, void* s_out, void* residual);
+                 const uint8_t* ns, void* y, void* s_out, void* residual, const int* run_if, int run_ticket,
+                 int* residual_mark);
 int wkv6_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* r, const void* k, const void* v,
                  const void* w, int per_token, const void* u, const uint32_t* length, const uint8_t* ns,
                  const void* dy, const void* ds_out, const void* residual, void* dr, void* dk, void* dv, void* dw,
-                 void* du, void* ds0);
+                 void* du, void* ds0, const int* run_if);
+size_t wkv6_chunk_residual_bytes(int B, int T, int H);
+int wkv6_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
+                   int per_token, const void* u, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+                   void* s_out, void* residual, int* residual_mark, int** flag, int* ticket);
+int wkv6_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
+                   int per_token, const void* u, const uint32_t* length, const uint8_t* ns, const void* dy, const void* ds_out,
+                   const void* residual, const int* residual_mark, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0);
 size_t wkv4_residual_bytes(int B, int T, int C);
 int wkv4_fwd(cudaStream_t st, int dtype, int B, int T, int C, const void* w, const void* u, const void* k, const void* v,
              const void* s0, const uint32_t* length, const uint8_t* ns, void* s_out, void* y, void* residual);
@@ -183,7 +191,13 @@ int b200wkv7_bwd(void* stream, int dtype, int B, int T, int H, int N, const void
 
 size_t b200wkv6_residual_bytes(int dtype, int B, int T, int H, int N) {
     if (check_dims(dtype, B, T, H, N) != B200WKV_OK) return 0;
-    return wkv6_seq_residual_bytes(B, T, H);
+    // fp32 uses the sequential kernels (an fp32 state every 16 tokens); bf16 uses the chunked tensor-core kernels (a
+    // bf16 state every 16 tokens) with the sequential ones as their fallback, so size for both, plus one word at
+    // the end that says which of the two formats the forward left
+    const size_t seq = wkv6_seq_residual_bytes(B, T, H);
+    if (dtype == B200WKV_F32) return seq;
+    const size_t chk = wkv6_chunk_residual_bytes(B, T, H);
+    return (seq > chk ? seq : chk) + kResidualMarkBytes;
 }
 
 int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int N, const void* r, const void* k,
@@ -194,10 +208,24 @@ int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int 
     if (st != B200WKV_OK) return st;
     if (version != 5 && version != 6) return B200WKV_EUNSUPPORTED;
     if (!r || !k || !v || !w || !u || !s0 || !length || !new_starts || !y || !s_out) return B200WKV_ENULL;
-    if (residual != nullptr && residual_bytes < wkv6_seq_residual_bytes(B, T, H)) return B200WKV_ERESIDUAL;
-    (void)flags;
+    if (residual != nullptr && residual_bytes < b200wkv6_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
+    if (dtype == B200WKV_BF16) {
+        int* mark = residual_mark_of(residual, b200wkv6_residual_bytes(dtype, B, T, H, N));
+        if (flags & B200WKV_FLAG_SEQUENTIAL)
+            return wkv6_seq_fwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, s0, length, new_starts, y,
+                                s_out, residual, nullptr, 0, mark);
+        // the chunked tensor-core kernel, and behind it the sequential kernel, which runs only if the chunked one met
+        // something outside its domain (it then redoes the whole call and marks the residual as its own)
+        int* flag = nullptr;
+        int ticket = 0;
+        st = wkv6_chunk_fwd((cudaStream_t)stream, B, T, H, r, k, v, w, version == 6, u, s0, length, new_starts, y, s_out,
+                            residual, mark, &flag, &ticket);
+        if (st != B200WKV_OK) return st;
+        return wkv6_seq_fwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, s0, length, new_starts, y,
+                            s_out, residual, flag, ticket, mark);
+    }
     return wkv6_seq_fwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, s0, length, new_starts, y,
-                        s_out, residual);
+                        s_out, residual, nullptr, 0, nullptr);
 }
 
 int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int N, const void* r, const void* k,
@@ -209,10 +237,19 @@ int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int 
     if (version != 5 && version != 6) return B200WKV_EUNSUPPORTED;
     if (!r || !k || !v || !w || !u || !s0 || !length || !new_starts || !residual || !dr || !dk || !dv || !dw || !du || !ds0)
         return B200WKV_ENULL;
-    if (residual_bytes < wkv6_seq_residual_bytes(B, T, H)) return B200WKV_ERESIDUAL;
+    if (residual_bytes < b200wkv6_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
     (void)flags;
+    if (dtype == B200WKV_BF16) {
+        // the forward's mark decides on the device which of the two runs; the other returns at once
+        const int* mark = residual_mark_of(const_cast<void*>(residual), b200wkv6_residual_bytes(dtype, B, T, H, N));
+        st = wkv6_chunk_bwd((cudaStream_t)stream, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy, ds_out, residual,
+                            mark, dr, dk, dv, dw, du, ds0);
+        if (st != B200WKV_OK) return st;
+        return wkv6_seq_bwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy, ds_out,
+                            residual, dr, dk, dv, dw, du, ds0, mark);
+    }
     return wkv6_seq_bwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy,
-                        ds_out, residual, dr, dk, dv, dw, du, ds0);
+                        ds_out, residual, dr, dk, dv, dw, du, ds0, nullptr);
 }
 
 size_t b200wkv4_residual_bytes(int dtype, int B, int T, int C) {

@@ -1,0 +1,700 @@
+// RWKV-5 / 5.2 / 6 WKV recurrence in chunks of 16 tokens on the tensor cores (bf16 I/O, fp32 state).
+//
+// State S[key i][value j];  y_t = r_t (S_{t-1} + diag(u) k_t^T v_t),  S_t = diag(d_t) S_{t-1} + k_t^T v_t  with the decay
+// d_t = exp(lw_t) per key channel (lw_t = w_t for RWKV-6, log of the head's constant for RWKV-5 / 5.2).  With the
+// inclusive cumulative log-decay c_t inside a chunk (c_{-1} = 0, c_m at the chunk's middle, c_C at its end):
+//     R0_t = r_t exp(c_{t-1})            K^_s = k_s exp(c_C - c_s)
+//     R~_t = r_t exp(c_{t-1} - c_m)      K~_s = k_s exp(c_m - c_s)         (referenced to the middle: |exponent| <= 8 tokens)
+//     A_ts = R~_t . K~_s  (s < t),  A_tt = sum_i r u k
+//     Y = R0 S0 + A V                    S_C = diag(exp(c_C)) S0 + K^^T V
+// A start flag on token p cuts every dependence of tokens >= p on tokens < p and on S0: masks on A, on the rows
+// of R0 and of K^, and on the carried state.  The state is held transposed, S^T[j][i], as mma.sync accumulator
+// tiles (fp32, each of the four warps 16 value rows): a tile is already in the register layout of the next
+// product's left operand, and the 16x16 score block A, computed by every warp for itself, is already in the
+// layout of a right operand, so nothing but the scaled operands passes through shared memory.  The chunk is 16
+// tokens because the per-channel decay is unbounded: referenced to the chunk's middle the scaling factors stay
+// below exp(8 |lw|), which fp32 / bf16 hold for |lw| <= 10 per token (decay >= 4.5e-5); a chunk beyond that, or a
+// `length` that is not a chunk boundary, makes the kernel leave its ticket in a flag and the token-sequential
+// kernels (wkv6_seq.cu) redo the call.  tcgen05 does not apply: its smallest tile is 64 tokens.
+//
+// Semantics: BaseRWKV.inner_loop of jaxrwkv, src/jaxrwkv/rwkv6.py:174-191, rwkv5_2.py:164-180, rwkv5.py:161-177.
+#include "common.cuh"
+#include "device_once.cuh"
+
+namespace b200wkv {
+
+int* wkv_call_flag(int* ticket);   // wkv7_chunk.cu: a slot of the per-device flag ring and a fresh ticket
+
+namespace {
+
+typedef __nv_bfloat16 bf;
+constexpr int kC6 = 16;          // tokens per chunk
+constexpr int PITCH = 72;        // bf16 per shared-memory row (144 bytes): 4-byte fragment reads and ldmatrix rows hit 32 banks
+constexpr int kStages6 = 3;
+constexpr float kMaxHalfDecay = 80.f;   // |sum of lw over half a chunk| the scaling can represent
+
+struct RawStage {
+    bf r[kC6][PITCH], k[kC6][PITCH], v[kC6][PITCH], w[kC6][PITCH];
+};
+
+__device__ __forceinline__ void cp_async16_zfill(void* dst_smem, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src), "r"(n)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
+// D(16x8, fp32) += A(16x16, bf16, row) B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t ld32(const bf* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+// ------------------------------------------------------------------ forward ---------
+struct Fwd6cSmem {
+    RawStage raw[kStages6];
+    bf rt[kC6][PITCH], kt[kC6][PITCH], r0[kC6][PITCH], kh[kC6][PITCH];   // R~, K~, R0, K^
+    bf ys[kC6][PITCH];                                                   // the chunk's outputs, token-major
+    float tot[2][kN];        // sum of lw over each half of the chunk
+    float wc[kN];            // exp(c_C), or 0 when a start flag lies in the chunk
+    float dpart[2][kC6];     // sum_i r u k per token, one partial per 32 channels
+    int seg[kC6];            // number of start flags at or before the token, inside the chunk
+    uint8_t ns[kStages6][kC6];
+};
+
+// One CTA of 128 threads per (batch, head).  ckpt: the state entering every chunk, bf16 [value j][key i], for
+// the backward (may be NULL).  The kernel gives up (flag := ticket, see the file header) on a length that is not
+// a chunk boundary and on a half-chunk decay beyond exp(-80).
+__global__ void __launch_bounds__(128)
+wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ k, const bf* __restrict__ v,
+                      const bf* __restrict__ w, int w_per_token, const bf* __restrict__ u, const bf* __restrict__ s0,
+                      const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts, bf* __restrict__ y,
+                      bf* __restrict__ s_out, bf* __restrict__ ckpt, int* __restrict__ flag, int ticket,
+                      int* __restrict__ residual_mark) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Fwd6cSmem& sm = *reinterpret_cast<Fwd6cSmem*>(smem_raw);
+    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int j0 = warp * 16;                                    // this warp's value rows of S^T
+    const size_t tok_stride = (size_t)H * kN;
+    const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
+    const size_t st_base = (size_t)bh * kN * kN;
+    const int L = min((int)length[bi], Tlen);
+    const int nC = (Tlen + kC6 - 1) / kC6;
+    if (bh == 0 && tid == 0 && residual_mark != nullptr) *residual_mark = 0;   // chunked format (so far)
+    if (L % kC6 != 0 && L != Tlen) {
+        if (tid == 0) atomicExch(flag, ticket);
+        return;
+    }
+    const int c_out = L > 0 ? (L - 1) / kC6 : -1;                // the returned state leaves this chunk
+
+    // S^T tiles: acc[ni][e] = S[i = 8 ni + 2 q + (e & 1)][j = j0 + g + 8 (e >> 1)]
+    float acc[8][4];
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            acc[ni][e] = __bfloat162float(s0[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)]);
+    auto write_state = [&](bf* dst) {                             // [key i][value j], as the caller keeps it
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                dst[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(acc[ni][e]);
+    };
+    if (L == 0) write_state(s_out);
+
+    const int srow = tid >> 3, spiece = (tid & 7) * 8;            // staging: one 16-byte piece of one token row per stream
+    auto issue = [&](int c) {
+        if (c < nC) {
+            RawStage& st = sm.raw[c % kStages6];
+            const int t = c * kC6 + srow;
+            const bool ok = t < Tlen;
+            const size_t off = seq_base + (size_t)(ok ? t : 0) * tok_stride + spiece;
+            cp_async16_zfill(&st.r[srow][spiece], r + off, ok);
+            cp_async16_zfill(&st.k[srow][spiece], k + off, ok);
+            cp_async16_zfill(&st.v[srow][spiece], v + off, ok);
+            if (w_per_token) cp_async16_zfill(&st.w[srow][spiece], w + off, ok);
+        }
+        cp_async_commit();
+    };
+    auto load_ns = [&](int c) -> uint8_t {
+        const int t = c * kC6 + tid;
+        return (tid < kC6 && c < nC && t < Tlen) ? new_starts[(size_t)bi * Tlen + t] : (uint8_t)0;
+    };
+    issue(0);
+    issue(1);
+    if (tid < kC6) {
+        sm.ns[0][tid] = load_ns(0);
+        sm.ns[1 % kStages6][tid] = load_ns(1);
+    }
+    uint8_t ns_ahead = load_ns(2);
+
+    // phase A ownership: channel ch, tokens 8 half .. 8 half + 7
+    const int ch = tid & 63, half = tid >> 6;
+    const float uu = __bfloat162float(u[(size_t)h * kN + ch]);
+    const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
+    bool bad = false;
+
+    for (int c = 0; c < nC; ++c) {
+        cp_async_wait<1>();
+        __syncthreads();          // chunk c has landed for everyone; the tiles of chunk c - 1 are no longer read
+        issue(c + 2);
+        if (tid < kC6) sm.ns[(c + 2) % kStages6][tid] = ns_ahead;
+        ns_ahead = load_ns(c + 3);
+        const RawStage& st = sm.raw[c % kStages6];
+        const int t0 = c * kC6;
+        // ---- outputs of the previous chunk to global memory
+        if (c > 0 && t0 - kC6 + srow < Tlen)
+            *reinterpret_cast<uint4*>(y + seq_base + (size_t)(t0 - kC6 + srow) * tok_stride + spiece) =
+                *reinterpret_cast<const uint4*>(&sm.ys[srow][spiece]);
+        // ---- the entering state for the backward
+        if (ckpt != nullptr) {
+            bf* dst = ckpt + ((size_t)bh * nC + c) * kN * kN;
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni) {
+                *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g) * kN + 8 * ni + 2 * q) = pack2(acc[ni][0], acc[ni][1]);
+                *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g + 8) * kN + 8 * ni + 2 * q) = pack2(acc[ni][2], acc[ni][3]);
+            }
+        }
+        // ---- phase A: cumulative log-decay and scaled operands
+        int seg_mine[8], seg_last;
+        {
+            int cnt = 0;
+#pragma unroll
+            for (int t = 0; t < kC6; ++t) {
+                cnt += sm.ns[c % kStages6][t] != 0;
+                if ((t >> 3) == half) seg_mine[t & 7] = cnt;      // resolved at compile time per unrolled t, selected by half
+                if (tid == t) sm.seg[t] = cnt;
+            }
+            seg_last = cnt;
+        }
+        float lw[8], cl[8];
+        float run = 0.f;
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const int t = 8 * half + tt;
+            const bool ok = t0 + t < Tlen;
+            lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
+            if (!(lw[tt] <= 0.f)) bad = true;      // a decay above 1 (or NaN) is outside what the scaling covers
+            run += lw[tt];
+            cl[tt] = run;
+        }
+        sm.tot[half][ch] = run;
+        // the operands need the other half's total: a barrier of the whole CTA
+        __syncthreads();
+        const float tot0 = sm.tot[0][ch], tot1 = sm.tot[1][ch];
+        if (fabsf(tot0) > kMaxHalfDecay || fabsf(tot1) > kMaxHalfDecay) bad = true;
+        const float c_m = fmaxf(tot0, -kMaxHalfDecay), c_C = c_m + fmaxf(tot1, -kMaxHalfDecay);
+        const float base = half ? c_m : 0.f;
+        if (half) sm.wc[ch] = seg_last == 0 ? __expf(c_C) : 0.f;
+        float dsum[8];
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const int t = 8 * half + tt;
+            const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
+            const float rv = __bfloat162float(st.r[t][ch]), kv = __bfloat162float(st.k[t][ch]);
+            sm.rt[t][ch] = __float2bfloat16_rn(rv * __expf(fminf(c_prev - c_m, kMaxHalfDecay)));
+            sm.kt[t][ch] = __float2bfloat16_rn(kv * __expf(fminf(c_m - c_t, kMaxHalfDecay)));
+            sm.r0[t][ch] = __float2bfloat16_rn(seg_mine[tt] == 0 ? rv * __expf(c_prev) : 0.f);
+            sm.kh[t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
+            dsum[tt] = rv * uu * kv;
+        }
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) dsum[tt] += __shfl_xor_sync(0xffffffffu, dsum[tt], m);
+        }
+        {
+            float mine = 0.f;     // after the butterflies every lane holds every sum: lane tt keeps the one of token tt
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) mine = lane == tt ? dsum[tt] : mine;
+            if (lane < 8) sm.dpart[warp & 1][8 * half + lane] = mine;
+        }
+        __syncthreads();
+
+        // ---- phase B: the products
+        uint32_t va[4];            // V^T of this warp: A fragments (M = value row, K = token)
+        {
+            const int mi = lane >> 3, r8 = lane & 7;
+            ldmatrix_x4_trans(va[0], va[1], va[2], va[3], &st.v[(mi >> 1) * 8 + r8][j0 + (mi & 1) * 8]);
+        }
+        float yacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};    // Y^T: rows value j, columns token t
+        float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};    // A: rows token t, columns token s
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t s_a0 = pack2(acc[2 * ks][0], acc[2 * ks][1]), s_a1 = pack2(acc[2 * ks][2], acc[2 * ks][3]);
+            const uint32_t s_a2 = pack2(acc[2 * ks + 1][0], acc[2 * ks + 1][1]), s_a3 = pack2(acc[2 * ks + 1][2], acc[2 * ks + 1][3]);
+            const uint32_t r_a0 = ld32(&sm.rt[g][16 * ks + 2 * q]), r_a1 = ld32(&sm.rt[g + 8][16 * ks + 2 * q]);
+            const uint32_t r_a2 = ld32(&sm.rt[g][16 * ks + 8 + 2 * q]), r_a3 = ld32(&sm.rt[g + 8][16 * ks + 8 + 2 * q]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                mma_bf16(yacc[nt], s_a0, s_a1, s_a2, s_a3, ld32(&sm.r0[8 * nt + g][16 * ks + 2 * q]),
+                         ld32(&sm.r0[8 * nt + g][16 * ks + 8 + 2 * q]));
+                mma_bf16(sacc[nt], r_a0, r_a1, r_a2, r_a3, ld32(&sm.kt[8 * nt + g][16 * ks + 2 * q]),
+                         ld32(&sm.kt[8 * nt + g][16 * ks + 8 + 2 * q]));
+            }
+        }
+        // masks: strictly earlier tokens of the same segment; the diagonal is the u term
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = g + 8 * (e >> 1), s = 8 * nt + 2 * q + (e & 1);
+                const bool keep = s < t && sm.seg[s] == sm.seg[t];
+                sacc[nt][e] = keep ? sacc[nt][e] : (s == t ? sm.dpart[0][t] + sm.dpart[1][t] : 0.f);
+            }
+        // Y^T += V^T A^T: the score tiles are the right operand as they are
+        mma_bf16(yacc[0], va[0], va[1], va[2], va[3], pack2(sacc[0][0], sacc[0][1]), pack2(sacc[1][0], sacc[1][1]));
+        mma_bf16(yacc[1], va[0], va[1], va[2], va[3], pack2(sacc[0][2], sacc[0][3]), pack2(sacc[1][2], sacc[1][3]));
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sm.ys[8 * nt + 2 * q + (e & 1)][j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(yacc[nt][e]);
+        // S^T <- S^T diag(exp(c_C)) [no start in the chunk] + V^T K^
+        {
+            const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                const float2 w0 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 2 * q]);
+                const float2 w1 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 8 + 2 * q]);
+                acc[2 * np][0] *= w0.x; acc[2 * np][1] *= w0.y; acc[2 * np][2] *= w0.x; acc[2 * np][3] *= w0.y;
+                acc[2 * np + 1][0] *= w1.x; acc[2 * np + 1][1] *= w1.y; acc[2 * np + 1][2] *= w1.x; acc[2 * np + 1][3] *= w1.y;
+                uint32_t b0, b1, b2, b3;        // key tiles 2 np (b0, b1) and 2 np + 1 (b2, b3)
+                ldmatrix_x4_trans(b0, b1, b2, b3, &sm.kh[(mi & 1) * 8 + r8][(2 * np + (mi >> 1)) * 8]);
+                mma_bf16(acc[2 * np], va[0], va[1], va[2], va[3], b0, b1);
+                mma_bf16(acc[2 * np + 1], va[0], va[1], va[2], va[3], b2, b3);
+            }
+        }
+        if (c == c_out) write_state(s_out);
+    }
+    __syncthreads();
+    {
+        const int t = (nC - 1) * kC6 + srow;
+        if (t < Tlen) *reinterpret_cast<uint4*>(y + seq_base + (size_t)t * tok_stride + spiece) = *reinterpret_cast<const uint4*>(&sm.ys[srow][spiece]);
+    }
+    if (bad) atomicExch(flag, ticket);
+}
+
+
+// ------------------------------------------------------------------ backward --------
+// Chunks in reverse order with the gradient of the state, dS^T[j][i], in accumulator tiles.  Per chunk, with the
+// forward's operands rebuilt from the raw rows and the entering state S0 read from the forward's checkpoint:
+//     dA = mask(dY V^T)                                   dd_t = dy_t . v_t  (its diagonal, the u term)
+//     dV  = A^T dY + K^ dS_C
+//     dR0 = dY S0^T        dR~ = dA K~        dK~ = dA^T R~        dK^ = V dS_C^T
+//     dr = dR0 exp(c_{t-1}) + dR~ exp(c_{t-1} - c_m) + dd u k        dk = dK~ exp(c_m - c_s) + dK^ exp(c_C - c_s) + dd u r
+//     dS0^T = dS_C^T diag(exp(c_C)) + dY^T R0
+// and the gradient of the log-decay from the positions at which each factor depends on the cumulative sum:
+//     dlw_tau = sum_{x >= tau} [ (r dr')_{x+1} - (k dk')_x ] + sum_s k dK^ exp(c_C - c_s) + exp(c_C) sum_j dS_C S0
+// (dr', dk' without the u terms; the two references to the middle cancel).  Every warp owns 16 channels of the
+// token-by-channel results and 16 value rows of dS^T, and computes the 16x16 score blocks for itself.
+struct BwdStage {
+    bf r[kC6][PITCH], k[kC6][PITCH], v[kC6][PITCH], w[kC6][PITCH], dy[kC6][PITCH];
+    bf s0[kN][PITCH];          // S0^T[j][i]
+};
+struct Bwd6cSmem {
+    BwdStage st[2];
+    bf ops[4][kC6][PITCH];     // R~, K~, R0, K^ while the products run; then dr, dk, dv, dw on their way out
+    bf ds[kN][PITCH];          // dS_C^T[j][i] in bf16, for the one product that contracts over j
+    float c[kC6][kN];          // inclusive cumulative log-decay
+    float ea[kC6][kN], eb[kC6][kN];   // r dr' and k dk' per token and channel
+    float tot[2][kN];
+    float wc[kN];              // exp(c_C), or 0 when a start flag lies in the chunk
+    float lump[kN];            // what every token of the chunk receives: the K^ references and the carried state
+    float gw[4][kN];           // sum_j dS_C S0 over each warp's value rows
+    float dpart[2][kC6];
+    int seg[kC6];
+    uint8_t ns[2][kC6];
+};
+
+__global__ void __launch_bounds__(128)
+wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ k, const bf* __restrict__ v,
+                      const bf* __restrict__ w, int w_per_token, const bf* __restrict__ u,
+                      const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
+                      const bf* __restrict__ dy, const bf* __restrict__ ds_out, const bf* __restrict__ ckpt,
+                      const int* __restrict__ residual_mark, bf* __restrict__ dr, bf* __restrict__ dk, bf* __restrict__ dv,
+                      bf* __restrict__ dw_tok, float* __restrict__ dw_head, float* __restrict__ du_head, bf* __restrict__ ds0) {
+    if (*residual_mark != 0) return;          // the forward fell back to the sequential kernels
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Bwd6cSmem& sm = *reinterpret_cast<Bwd6cSmem*>(smem_raw);
+    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3, mi = lane >> 3, r8 = lane & 7;
+    const int j0 = warp * 16;                 // value rows of dS^T, and key channels of the token-by-channel results
+    const size_t tok_stride = (size_t)H * kN;
+    const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
+    const size_t st_base = (size_t)bh * kN * kN;
+    const int L = min((int)length[bi], Tlen);
+    const int nC = (Tlen + kC6 - 1) / kC6;
+    const int c_out = L > 0 ? (L - 1) / kC6 : -1;
+
+    float acc[8][4];
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[ni][e] = 0.f;
+    auto add_ds_out = [&]() {
+        if (ds_out == nullptr) return;
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                acc[ni][e] += __bfloat162float(ds_out[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)]);
+    };
+
+    const int srow = tid >> 3, spiece = (tid & 7) * 8;
+    auto issue = [&](int c, int stage) {
+        if (c >= 0) {
+            BwdStage& st = sm.st[stage];
+            const int t = c * kC6 + srow;
+            const bool ok = t < Tlen;
+            const size_t off = seq_base + (size_t)(ok ? t : 0) * tok_stride + spiece;
+            cp_async16_zfill(&st.r[srow][spiece], r + off, ok);
+            cp_async16_zfill(&st.k[srow][spiece], k + off, ok);
+            cp_async16_zfill(&st.v[srow][spiece], v + off, ok);
+            if (w_per_token) cp_async16_zfill(&st.w[srow][spiece], w + off, ok);
+            cp_async16_zfill(&st.dy[srow][spiece], dy != nullptr ? dy + off : r + off, ok && dy != nullptr);
+            const bf* src = ckpt + ((size_t)bh * nC + c) * kN * kN;
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) cp_async16_zfill(&st.s0[srow + 16 * rr][spiece], src + (size_t)(srow + 16 * rr) * kN + spiece, true);
+        }
+        cp_async_commit();
+    };
+    auto load_ns = [&](int c) -> uint8_t {
+        const int t = c * kC6 + tid;
+        return (tid < kC6 && c >= 0 && t < Tlen) ? new_starts[(size_t)bi * Tlen + t] : (uint8_t)0;
+    };
+    issue(nC - 1, 0);
+    if (tid < kC6) sm.ns[0][tid] = load_ns(nC - 1);
+    uint8_t ns_ahead = load_ns(nC - 2);
+
+    const int ch = tid & 63, half = tid >> 6;
+    const float uu_a = __bfloat162float(u[(size_t)h * kN + ch]);
+    const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
+    float u_col[2][2];                         // u of this thread's four result columns
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) u_col[nt][e] = __bfloat162float(u[(size_t)h * kN + j0 + 8 * nt + 2 * q + e]);
+    float du_acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    float dw_acc = 0.f;                        // constant decay: sum over tokens of the log-decay gradient (thread ch < 64)
+
+    for (int c = nC - 1, it = 0; c >= 0; --c, ++it) {
+        const int stage = it & 1;
+        cp_async_wait<0>();
+        __syncthreads();                                              // S1
+        issue(c - 1, stage ^ 1);
+        if (tid < kC6) sm.ns[stage ^ 1][tid] = ns_ahead;
+        ns_ahead = load_ns(c - 2);
+        const BwdStage& st = sm.st[stage];
+        const int t0 = c * kC6;
+        if (c == c_out) add_ds_out();
+        // dS_C^T in bf16 for the product that contracts over value rows
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni) {
+            *reinterpret_cast<uint32_t*>(&sm.ds[j0 + g][8 * ni + 2 * q]) = pack2(acc[ni][0], acc[ni][1]);
+            *reinterpret_cast<uint32_t*>(&sm.ds[j0 + g + 8][8 * ni + 2 * q]) = pack2(acc[ni][2], acc[ni][3]);
+        }
+        // ---- phase A: as in the forward
+        int seg_mine[8], seg_last;
+        {
+            int cnt = 0;
+#pragma unroll
+            for (int t = 0; t < kC6; ++t) {
+                cnt += sm.ns[stage][t] != 0;
+                if ((t >> 3) == half) seg_mine[t & 7] = cnt;
+                if (tid == t) sm.seg[t] = cnt;
+            }
+            seg_last = cnt;
+        }
+        float lw[8], cl[8];
+        float run = 0.f;
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const int t = 8 * half + tt;
+            const bool ok = t0 + t < Tlen;
+            lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
+            run += lw[tt];
+            cl[tt] = run;
+        }
+        sm.tot[half][ch] = run;
+        __syncthreads();                                              // S2
+        {
+            const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
+            const float base = half ? c_m : 0.f;
+            if (half) sm.wc[ch] = seg_last == 0 ? __expf(c_C) : 0.f;
+            float dsum[8];
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+                const int t = 8 * half + tt;
+                const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
+                const float rv = __bfloat162float(st.r[t][ch]), kv = __bfloat162float(st.k[t][ch]);
+                sm.c[t][ch] = c_t;
+                sm.ops[0][t][ch] = __float2bfloat16_rn(rv * __expf(fminf(c_prev - c_m, kMaxHalfDecay)));
+                sm.ops[1][t][ch] = __float2bfloat16_rn(kv * __expf(fminf(c_m - c_t, kMaxHalfDecay)));
+                sm.ops[2][t][ch] = __float2bfloat16_rn(seg_mine[tt] == 0 ? rv * __expf(c_prev) : 0.f);
+                sm.ops[3][t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
+                dsum[tt] = rv * uu_a * kv;
+            }
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+#pragma unroll
+                for (int m = 1; m < 32; m <<= 1) dsum[tt] += __shfl_xor_sync(0xffffffffu, dsum[tt], m);
+            }
+            float mine = 0.f;
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) mine = lane == tt ? dsum[tt] : mine;
+            if (lane < 8) sm.dpart[warp & 1][8 * half + lane] = mine;
+        }
+        __syncthreads();                                              // S3
+        const bf (*Rt)[PITCH] = sm.ops[0];
+        const bf (*Kt)[PITCH] = sm.ops[1];
+        const bf (*R0)[PITCH] = sm.ops[2];
+        const bf (*Kh)[PITCH] = sm.ops[3];
+
+        // ---- the 16x16 blocks: dA (t x s), dA^T (s x t), A^T (s x t)
+        float dA[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dAT[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float AT[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        uint32_t dya[4][4], vaf[4][4];        // dY and V as left operands (rows token, K = value j), all four K steps
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            dya[ks][0] = ld32(&st.dy[g][16 * ks + 2 * q]);      dya[ks][1] = ld32(&st.dy[g + 8][16 * ks + 2 * q]);
+            dya[ks][2] = ld32(&st.dy[g][16 * ks + 8 + 2 * q]);  dya[ks][3] = ld32(&st.dy[g + 8][16 * ks + 8 + 2 * q]);
+            vaf[ks][0] = ld32(&st.v[g][16 * ks + 2 * q]);       vaf[ks][1] = ld32(&st.v[g + 8][16 * ks + 2 * q]);
+            vaf[ks][2] = ld32(&st.v[g][16 * ks + 8 + 2 * q]);   vaf[ks][3] = ld32(&st.v[g + 8][16 * ks + 8 + 2 * q]);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t k_a0 = ld32(&Kt[g][16 * ks + 2 * q]), k_a1 = ld32(&Kt[g + 8][16 * ks + 2 * q]);
+            const uint32_t k_a2 = ld32(&Kt[g][16 * ks + 8 + 2 * q]), k_a3 = ld32(&Kt[g + 8][16 * ks + 8 + 2 * q]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                // as right operands a row-major [token][channel] tile is read along its rows: n = token, k = channel
+                mma_bf16(dA[nt], dya[ks][0], dya[ks][1], dya[ks][2], dya[ks][3], ld32(&st.v[8 * nt + g][16 * ks + 2 * q]),
+                         ld32(&st.v[8 * nt + g][16 * ks + 8 + 2 * q]));
+                mma_bf16(dAT[nt], vaf[ks][0], vaf[ks][1], vaf[ks][2], vaf[ks][3], ld32(&st.dy[8 * nt + g][16 * ks + 2 * q]),
+                         ld32(&st.dy[8 * nt + g][16 * ks + 8 + 2 * q]));
+                mma_bf16(AT[nt], k_a0, k_a1, k_a2, k_a3, ld32(&Rt[8 * nt + g][16 * ks + 2 * q]),
+                         ld32(&Rt[8 * nt + g][16 * ks + 8 + 2 * q]));
+            }
+        }
+        // dd of this thread's two token rows: the diagonal of dA sits in lane 4 g + g / 2
+        float dd_lo, dd_hi;
+        {
+            const float cand_lo = (g & 1) ? dA[0][1] : dA[0][0], cand_hi = (g & 1) ? dA[1][3] : dA[1][2];
+            const int src = (lane & ~3) | (g >> 1);
+            dd_lo = __shfl_sync(0xffffffffu, cand_lo, src);
+            dd_hi = __shfl_sync(0xffffffffu, cand_hi, src);
+        }
+        int seg_r[2] = {sm.seg[g], sm.seg[g + 8]};
+        const int seg_end = sm.seg[kC6 - 1];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = g + 8 * (e >> 1), col = 8 * nt + 2 * q + (e & 1);
+                const bool same = sm.seg[col] == seg_r[e >> 1];
+                dA[nt][e] = (col < row && same) ? dA[nt][e] : 0.f;                       // rows t, columns s < t
+                dAT[nt][e] = (row < col && same) ? dAT[nt][e] : 0.f;                     // rows s, columns t > s
+                AT[nt][e] = (row < col && same) ? AT[nt][e] : (row == col ? sm.dpart[0][row] + sm.dpart[1][row] : 0.f);
+            }
+        // ---- dV (s x j of this warp) = A^T dY + K^ dS_C
+        float dV[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, &st.dy[(mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
+            const uint32_t a0 = pack2(AT[0][0], AT[0][1]), a1 = pack2(AT[0][2], AT[0][3]);
+            const uint32_t a2 = pack2(AT[1][0], AT[1][1]), a3 = pack2(AT[1][2], AT[1][3]);
+            mma_bf16(dV[0], a0, a1, a2, a3, b0, b1);
+            mma_bf16(dV[1], a0, a1, a2, a3, b2, b3);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t h0 = ld32(&Kh[g][16 * ks + 2 * q]), h1 = ld32(&Kh[g + 8][16 * ks + 2 * q]);
+                const uint32_t h2 = ld32(&Kh[g][16 * ks + 8 + 2 * q]), h3 = ld32(&Kh[g + 8][16 * ks + 8 + 2 * q]);
+                // dS_C^T tiles as right operand: K = key channel (their columns), n = value row (their rows)
+                mma_bf16(dV[0], h0, h1, h2, h3, pack2(acc[2 * ks][0], acc[2 * ks][1]), pack2(acc[2 * ks + 1][0], acc[2 * ks + 1][1]));
+                mma_bf16(dV[1], h0, h1, h2, h3, pack2(acc[2 * ks][2], acc[2 * ks][3]), pack2(acc[2 * ks + 1][2], acc[2 * ks + 1][3]));
+            }
+        }
+        // ---- the token x channel results for this warp's 16 key channels
+        float dR0[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dRt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float dKt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dKh[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, &st.s0[16 * ks + (mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
+            mma_bf16(dR0[0], dya[ks][0], dya[ks][1], dya[ks][2], dya[ks][3], b0, b1);
+            mma_bf16(dR0[1], dya[ks][0], dya[ks][1], dya[ks][2], dya[ks][3], b2, b3);
+            ldmatrix_x4_trans(b0, b1, b2, b3, &sm.ds[16 * ks + (mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
+            mma_bf16(dKh[0], vaf[ks][0], vaf[ks][1], vaf[ks][2], vaf[ks][3], b0, b1);
+            mma_bf16(dKh[1], vaf[ks][0], vaf[ks][1], vaf[ks][2], vaf[ks][3], b2, b3);
+        }
+        {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, &Kt[(mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
+            uint32_t a0 = pack2(dA[0][0], dA[0][1]), a1 = pack2(dA[0][2], dA[0][3]), a2 = pack2(dA[1][0], dA[1][1]), a3 = pack2(dA[1][2], dA[1][3]);
+            mma_bf16(dRt[0], a0, a1, a2, a3, b0, b1);
+            mma_bf16(dRt[1], a0, a1, a2, a3, b2, b3);
+            ldmatrix_x4_trans(b0, b1, b2, b3, &Rt[(mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
+            a0 = pack2(dAT[0][0], dAT[0][1]); a1 = pack2(dAT[0][2], dAT[0][3]); a2 = pack2(dAT[1][0], dAT[1][1]); a3 = pack2(dAT[1][2], dAT[1][3]);
+            mma_bf16(dKt[0], a0, a1, a2, a3, b0, b1);
+            mma_bf16(dKt[1], a0, a1, a2, a3, b2, b3);
+        }
+        // ---- sum_j dS_C[i][j] S0[i][j] over this warp's value rows
+        {
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni) {
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.s0[j0 + g][8 * ni + 2 * q]));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.s0[j0 + g + 8][8 * ni + 2 * q]));
+                float p0 = acc[ni][0] * lo.x + acc[ni][2] * hi.x, p1 = acc[ni][1] * lo.y + acc[ni][3] * hi.y;
+#pragma unroll
+                for (int m = 4; m < 32; m <<= 1) {
+                    p0 += __shfl_xor_sync(0xffffffffu, p0, m);
+                    p1 += __shfl_xor_sync(0xffffffffu, p1, m);
+                }
+                if (g == 0) *reinterpret_cast<float2*>(&sm.gw[warp][8 * ni + 2 * q]) = make_float2(p0, p1);
+            }
+        }
+        // ---- dS0^T = dS_C^T diag(exp(c_C)) [no start in the chunk] + dY^T R0
+        {
+            uint32_t ya[4];
+            ldmatrix_x4_trans(ya[0], ya[1], ya[2], ya[3], &st.dy[(mi >> 1) * 8 + r8][j0 + (mi & 1) * 8]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                const float2 w0 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 2 * q]);
+                const float2 w1 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 8 + 2 * q]);
+                acc[2 * np][0] *= w0.x; acc[2 * np][1] *= w0.y; acc[2 * np][2] *= w0.x; acc[2 * np][3] *= w0.y;
+                acc[2 * np + 1][0] *= w1.x; acc[2 * np + 1][1] *= w1.y; acc[2 * np + 1][2] *= w1.x; acc[2 * np + 1][3] *= w1.y;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, &R0[(mi & 1) * 8 + r8][(2 * np + (mi >> 1)) * 8]);
+                mma_bf16(acc[2 * np], ya[0], ya[1], ya[2], ya[3], b0, b1);
+                mma_bf16(acc[2 * np + 1], ya[0], ya[1], ya[2], ya[3], b2, b3);
+            }
+        }
+        __syncthreads();                                              // S4: nobody reads the operand tiles any more
+        // ---- epilogue: rows t = g, g + 8; columns i = j0 + 8 nt + 2 q + (e & 1)
+        {
+            float lump_part[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int t = g + 8 * (e >> 1), i = j0 + 8 * nt + 2 * q + (e & 1);
+                    const float c_t = sm.c[t][i], c_prev = t > 0 ? sm.c[t - 1][i] : 0.f, c_m = sm.c[7][i], c_C = sm.c[kC6 - 1][i];
+                    const float rv = __bfloat162float(st.r[t][i]), kv = __bfloat162float(st.k[t][i]);
+                    const float dd = (e >> 1) ? dd_hi : dd_lo, uc = u_col[nt][e & 1];
+                    const int sg = seg_r[e >> 1];
+                    const float drp = (sg == 0 ? dR0[nt][e] * __expf(c_prev) : 0.f) + dRt[nt][e] * __expf(fminf(c_prev - c_m, kMaxHalfDecay));
+                    const float kh_part = sg == seg_end ? dKh[nt][e] * __expf(c_C - c_t) : 0.f;
+                    const float dkp = dKt[nt][e] * __expf(fminf(c_m - c_t, kMaxHalfDecay)) + kh_part;
+                    sm.ops[0][t][i] = __float2bfloat16_rn(fmaf(dd * uc, kv, drp));
+                    sm.ops[1][t][i] = __float2bfloat16_rn(fmaf(dd * uc, rv, dkp));
+                    sm.ea[t][i] = rv * drp;
+                    sm.eb[t][i] = kv * dkp;
+                    lump_part[nt][e & 1] += kv * kh_part;
+                    du_acc[nt][e & 1] = fmaf(dd * rv, kv, du_acc[nt][e & 1]);
+                    sm.ops[2][t][i] = __float2bfloat16_rn(dV[nt][e]);      // dV: rows s = t, columns j = i (same index arithmetic)
+                }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float p = lump_part[nt][e];
+#pragma unroll
+                    for (int m = 4; m < 32; m <<= 1) p += __shfl_xor_sync(0xffffffffu, p, m);
+                    const int i = j0 + 8 * nt + 2 * q + e;
+                    if (g == 0) sm.lump[i] = p + (sm.gw[0][i] + sm.gw[1][i] + sm.gw[2][i] + sm.gw[3][i]) * sm.wc[i];
+                }
+        }
+        __syncthreads();                                              // S5
+        if (tid < kN) {
+            // suffix sums over the chunk's 16 positions: the log-decay of token tau acts on every cumulative sum c_x, x >= tau
+            float run2 = sm.lump[tid];
+#pragma unroll
+            for (int x = kC6 - 1; x >= 0; --x) {
+                run2 += (x + 1 < kC6 ? sm.ea[x + 1][tid] : 0.f) - sm.eb[x][tid];
+                if (w_per_token) sm.ops[3][x][tid] = __float2bfloat16_rn(run2);
+                else if (t0 + x < Tlen) dw_acc += run2;
+            }
+        }
+        __syncthreads();                                              // S6
+        {
+            const int t = t0 + srow;
+            if (t < Tlen) {
+                const size_t off = seq_base + (size_t)t * tok_stride + spiece;
+                *reinterpret_cast<uint4*>(dr + off) = *reinterpret_cast<const uint4*>(&sm.ops[0][srow][spiece]);
+                *reinterpret_cast<uint4*>(dk + off) = *reinterpret_cast<const uint4*>(&sm.ops[1][srow][spiece]);
+                *reinterpret_cast<uint4*>(dv + off) = *reinterpret_cast<const uint4*>(&sm.ops[2][srow][spiece]);
+                if (w_per_token) *reinterpret_cast<uint4*>(dw_tok + off) = *reinterpret_cast<const uint4*>(&sm.ops[3][srow][spiece]);
+            }
+        }
+    }
+    if (L == 0) add_ds_out();
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            ds0[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(acc[ni][e]);
+    // du: sum over this thread's token rows, then over the eight row groups of the warp
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float p = du_acc[nt][e];
+#pragma unroll
+            for (int m = 4; m < 32; m <<= 1) p += __shfl_xor_sync(0xffffffffu, p, m);
+            if (g == 0) du_head[(size_t)bh * kN + j0 + 8 * nt + 2 * q + e] = p;
+        }
+    if (!w_per_token && tid < kN) dw_head[(size_t)bh * kN + tid] = dw_acc / __bfloat162float(w[(size_t)h * kN + tid]);
+}
+
+}  // namespace
+
+size_t wkv6_chunk_residual_bytes(int B, int T, int H) {
+    return (size_t)B * H * ((T + kC6 - 1) / kC6) * kN * kN * sizeof(bf);
+}
+
+int wkv6_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
+                   int per_token, const void* u, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
+                   void* s_out, void* residual, int* residual_mark, int** flag, int* ticket) {
+    static DeviceOnce smem_attr;
+    if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv6_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Fwd6cSmem)); }))
+        return B200WKV_ELAUNCH;
+    *flag = wkv_call_flag(ticket);
+    if (*flag == nullptr) return B200WKV_ELAUNCH;
+    wkv6_chunk_fwd_kernel<<<B * H, 128, sizeof(Fwd6cSmem), st>>>(T, H, (const bf*)r, (const bf*)k, (const bf*)v, (const bf*)w, per_token,
+                                                                (const bf*)u, (const bf*)s0, length, ns, (bf*)y, (bf*)s_out,
+                                                                (bf*)residual, *flag, *ticket, residual_mark);
+    return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+}
+
+int wkv6_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
+                   int per_token, const void* u, const uint32_t* length, const uint8_t* ns, const void* dy, const void* ds_out,
+                   const void* residual, const int* residual_mark, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0) {
+    static DeviceOnce smem_attr;
+    if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv6_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd6cSmem)); }))
+        return B200WKV_ELAUNCH;
+    wkv6_chunk_bwd_kernel<<<B * H, 128, sizeof(Bwd6cSmem), st>>>(T, H, (const bf*)r, (const bf*)k, (const bf*)v, (const bf*)w, per_token,
+                                                                (const bf*)u, length, ns, (const bf*)dy, (const bf*)ds_out,
+                                                                (const bf*)residual, residual_mark, (bf*)dr, (bf*)dk, (bf*)dv,
+                                                                per_token ? (bf*)dw : nullptr, per_token ? nullptr : (float*)dw,
+                                                                (float*)du, (bf*)ds0);
+    return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+}
+
+}  // namespace b200wkv

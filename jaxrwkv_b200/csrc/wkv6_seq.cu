@@ -36,7 +36,12 @@ __global__ void __launch_bounds__(192, 4)
 wkv6_seq_fwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                     const T* __restrict__ w, int w_per_token, const T* __restrict__ u, const T* __restrict__ s0,
                     const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts, T* __restrict__ y,
-                    T* __restrict__ s_out, float* __restrict__ ckpt) {
+                    T* __restrict__ s_out, float* __restrict__ ckpt, const int* __restrict__ run_if, int run_ticket,
+                    int* __restrict__ residual_mark) {
+    // As the fallback behind the chunked kernel: run only when that kernel left its ticket in *run_if, and
+    // mark the residual as being in this kernel's format.
+    if (run_if != nullptr && *run_if != run_ticket) return;
+    if (residual_mark != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *residual_mark = 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Fwd6Smem& sm = *reinterpret_cast<Fwd6Smem*>(smem_raw);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -166,7 +171,9 @@ wkv6_seq_bwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restric
                     const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
                     const T* __restrict__ dy, const T* __restrict__ ds_out, const float* __restrict__ ckpt,
                     T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv, T* __restrict__ dw_tok,
-                    float* __restrict__ dw_head, float* __restrict__ du_head, T* __restrict__ ds0) {
+                    float* __restrict__ dw_head, float* __restrict__ du_head, T* __restrict__ ds0,
+                    const int* __restrict__ run_if) {
+    if (run_if != nullptr && *run_if == 0) return;   // the residual is in the chunked kernels' format
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Bwd6Smem& sm = *reinterpret_cast<Bwd6Smem*>(smem_raw);
     const int bh = blockIdx.x, bi = bh / H, h = bh % H;
@@ -375,20 +382,22 @@ wkv6_seq_bwd_kernel(int Tlen, int H, const T* __restrict__ r, const T* __restric
 template <typename T>
 int launch_fwd6(cudaStream_t st, int B, int Tlen, int H, const void* r, const void* k, const void* v, const void* w,
                 int per_token, const void* u, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
-                void* s_out, void* residual) {
+                void* s_out, void* residual, const int* run_if, int run_ticket, int* residual_mark) {
     auto kern = wkv6_seq_fwd_kernel<T>;
     static DeviceOnce smem_attr;   // one per template instance; the attribute is per device
     if (!smem_attr.ok([kern]() { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Fwd6Smem)); }))
         return B200WKV_ELAUNCH;
     kern<<<B * H, 192, sizeof(Fwd6Smem), st>>>(Tlen, H, (const T*)r, (const T*)k, (const T*)v, (const T*)w, per_token,
-                                               (const T*)u, (const T*)s0, length, ns, (T*)y, (T*)s_out, (float*)residual);
+                                               (const T*)u, (const T*)s0, length, ns, (T*)y, (T*)s_out, (float*)residual,
+                                               run_if, run_ticket, residual_mark);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
 template <typename T>
 int launch_bwd6(cudaStream_t st, int B, int Tlen, int H, const void* r, const void* k, const void* v, const void* w,
                 int per_token, const void* u, const uint32_t* length, const uint8_t* ns, const void* dy,
-                const void* ds_out, const void* residual, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0) {
+                const void* ds_out, const void* residual, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0,
+                const int* run_if) {
     auto kern = wkv6_seq_bwd_kernel<T>;
     static DeviceOnce smem_attr;   // one per template instance; the attribute is per device
     if (!smem_attr.ok([kern]() { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd6Smem)); }))
@@ -397,7 +406,7 @@ int launch_bwd6(cudaStream_t st, int B, int Tlen, int H, const void* r, const vo
                                                (const T*)u, length, ns, (const T*)dy, (const T*)ds_out,
                                                (const float*)residual, (T*)dr, (T*)dk, (T*)dv,
                                                per_token ? (T*)dw : nullptr, per_token ? nullptr : (float*)dw,
-                                               (float*)du, (T*)ds0);
+                                               (float*)du, (T*)ds0, run_if);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 }  // namespace
@@ -408,18 +417,22 @@ size_t wkv6_seq_residual_bytes(int B, int T, int H) {
 
 int wkv6_seq_fwd(cudaStream_t st, int dtype, int B, int T, int H, const void* r, const void* k, const void* v,
                  const void* w, int per_token, const void* u, const void* s0, const uint32_t* length,
-                 const uint8_t* ns, void* y, void* s_out, void* residual) {
-    if (dtype == B200WKV_F32) return launch_fwd6<float>(st, B, T, H, r, k, v, w, per_token, u, s0, length, ns, y, s_out, residual);
-    return launch_fwd6<__nv_bfloat16>(st, B, T, H, r, k, v, w, per_token, u, s0, length, ns, y, s_out, residual);
+                 const uint8_t* ns, void* y, void* s_out, void* residual, const int* run_if, int run_ticket,
+                 int* residual_mark) {
+    if (dtype == B200WKV_F32)
+        return launch_fwd6<float>(st, B, T, H, r, k, v, w, per_token, u, s0, length, ns, y, s_out, residual, run_if, run_ticket, residual_mark);
+    return launch_fwd6<__nv_bfloat16>(st, B, T, H, r, k, v, w, per_token, u, s0, length, ns, y, s_out, residual, run_if, run_ticket,
+                                      residual_mark);
 }
 
 int wkv6_seq_bwd(cudaStream_t st, int dtype, int B, int T, int H, const void* r, const void* k, const void* v,
                  const void* w, int per_token, const void* u, const uint32_t* length, const uint8_t* ns,
                  const void* dy, const void* ds_out, const void* residual, void* dr, void* dk, void* dv, void* dw,
-                 void* du, void* ds0) {
+                 void* du, void* ds0, const int* run_if) {
     if (dtype == B200WKV_F32)
-        return launch_bwd6<float>(st, B, T, H, r, k, v, w, per_token, u, length, ns, dy, ds_out, residual, dr, dk, dv, dw, du, ds0);
-    return launch_bwd6<__nv_bfloat16>(st, B, T, H, r, k, v, w, per_token, u, length, ns, dy, ds_out, residual, dr, dk, dv, dw, du, ds0);
+        return launch_bwd6<float>(st, B, T, H, r, k, v, w, per_token, u, length, ns, dy, ds_out, residual, dr, dk, dv, dw, du, ds0, run_if);
+    return launch_bwd6<__nv_bfloat16>(st, B, T, H, r, k, v, w, per_token, u, length, ns, dy, ds_out, residual, dr, dk, dv, dw, du, ds0,
+                                      run_if);
 }
 
 }  // namespace b200wkv

@@ -525,6 +525,16 @@ static int* range_flag_ring() {
     return addr[dev];
 }
 
+// A slot of the ring and a ticket no earlier call used (never 0, so untouched memory cannot match); NULL on failure.
+int* wkv_call_flag(int* ticket) {
+    static std::atomic<unsigned> tickets{1};
+    int* ring = range_flag_ring();
+    if (ring == nullptr) return nullptr;
+    const unsigned t = tickets.fetch_add(1);
+    *ticket = (int)(t | 0x40000000u);
+    return ring + (t & 63u);
+}
+
 int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const void* r, const void* k, const void* v,
                    const void* a, const void* b, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
                    void* s_out, void* residual, int* residual_mark, int** range_flag, int* range_ticket) {
@@ -532,12 +542,8 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     static DeviceOnce smem_attr;   // the opt-in to large dynamic shared memory is a per-device function attribute
     if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv7_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); }))
         return B200WKV_ELAUNCH;
-    static std::atomic<unsigned> tickets{1};
-    int* ring = range_flag_ring();
-    if (ring == nullptr) return B200WKV_ELAUNCH;
-    const unsigned ticket = tickets.fetch_add(1);
-    *range_flag = ring + (ticket & 63u);
-    *range_ticket = (int)(ticket | 0x40000000u);   // never 0, so untouched memory cannot match
+    *range_flag = wkv_call_flag(range_ticket);
+    if (*range_flag == nullptr) return B200WKV_ELAUNCH;
     const CarryLayout lay = carry_layout(B, T, H);
     StreamMaps maps;
     const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]

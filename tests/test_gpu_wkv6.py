@@ -31,7 +31,7 @@ def dev(d, dtype):
     return {n: torch.tensor(d[n], dtype=torch.float32).to(dtype).cuda() for n in NAMES}
 
 
-def check(version, d, dtype, seed=0):
+def check(version, d, dtype, seed=0, tol_dw=None):
     t = dev(d, dtype)
     length, ns = flags(d)
     leaves = [t[n].clone().requires_grad_(True) for n in NAMES]
@@ -49,7 +49,7 @@ def check(version, d, dtype, seed=0):
     ref = oracle.wkv6_bwd_batched(*rounded, d["length"], d["new_starts"], npf(gy), npf(gs), version)
     for n, leaf, gref in zip(("dr", "dk", "dv", "dw", "du", "ds0"), leaves, ref):
         e = rel_err(npf(leaf.grad).reshape(gref.shape), gref)
-        assert e < tol, (n, e)
+        assert e < (tol_dw if (n == "dw" and tol_dw is not None) else tol), (n, e)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -152,3 +152,72 @@ def test_config3_full_size_backward():
             if a is not None:
                 e = rel_err(npf(a).reshape(b.shape), b)
                 assert e < 2e-2, (n, bi, hh, e)
+
+
+def _residual_mark(res):
+    """Last 16 bytes of the bf16 residual: 0 = written by the chunked kernels, 1 = by the sequential ones."""
+    return int(res[-1][-16:].view(torch.int32)[0].item())
+
+
+def _fwd_mark(version, d):
+    """Which kernels a bf16 forward of ``d`` uses (through the batched host call, which returns the residual)."""
+    t = dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    H = t["r"].shape[2]
+    w = t["w"] if version == "6" else fam._expand_hn(t["w"], H, 64, torch.bfloat16)
+    u = fam._expand_hn(t["u"], H, 64, torch.bfloat16)
+    w = w.reshape(t["r"].shape) if version == "6" else w
+    _, res = fam.batched_wkv6_fwd(version, t["r"], t["k"], t["v"], w, u, t["s0"], length.cuda(), ns.cuda(), t["r"].shape[0])
+    return _residual_mark(res)
+
+
+@pytest.mark.parametrize("version", ["6", "5_2", "5"])
+@pytest.mark.parametrize("T", [16, 48, 70, 200])
+def test_chunked_kernels_fwd_bwd(version, T):
+    """Shapes the 16-token tensor-core kernels take themselves (lengths 0, a multiple of 16, or T; T itself need not be
+    one): start flags at chunk boundaries, inside chunks, adjacent, on the last token; the cotangent of the returned
+    state entering in the middle of the sequence; all against the oracle, and the residual says which kernels ran."""
+    rng = np.random.default_rng(T)
+    starts = [sorted(set(rng.integers(0, T, size=3).tolist())), [0, 16 % T, T - 1], [T // 2, min(T // 2 + 1, T - 1)], []]
+    lengths = [T, (T // 16) * 16 if T >= 32 else T, 0, 16]
+    d = case(version, 4, T, 2, seed=900 + T, starts=starts, lengths=lengths, s0_scale=0.5)
+    assert _fwd_mark(version, d) == 0
+    # The gradient of a CONSTANT decay (versions 5, 5.2) is the sum over all tokens of per-token log-decay gradients
+    # that are themselves differences of bf16 tensor-core products; the terms largely cancel, so their rounding
+    # does not: 2-3 % of the result here, against 1 % for the fp32 sequential kernels.  Per-token gradients
+    # (version 6) stay inside the common bf16 tolerance.
+    check(version, d, torch.bfloat16, tol_dw=None if version == "6" else 4e-2)
+
+
+def test_chunked_kernels_fall_back_per_call():
+    """A length inside a chunk, a decay above 1 and a decay below exp(-10) per token are outside the chunked kernels'
+    domain: the call is redone by the sequential kernels (mark 1) and still matches the oracle."""
+    d = case("6", 2, 64, 2, seed=31, lengths=[64, 37])
+    assert _fwd_mark("6", d) == 1
+    check("6", d, torch.bfloat16)
+    d = case("6", 2, 64, 2, seed=32)
+    d["w"][1, 16:32] = -12.0                                   # log-decay: exp(-12) per token, -96 over eight tokens
+    assert _fwd_mark("6", d) == 1
+    check("6", d, torch.bfloat16)
+    d = case("6", 2, 64, 2, seed=33)
+    d["w"][0, 5] = 0.25                                        # a decay above 1
+    assert _fwd_mark("6", d) == 1
+    check("6", d, torch.bfloat16)
+    d = case("6", 2, 64, 2, seed=34)
+    d["w"][:] = np.maximum(d["w"], -9.0)                       # strong but representable decays stay chunked
+    d["w"][0, 8:24] = -9.0
+    assert _fwd_mark("6", d) == 0
+    check("6", d, torch.bfloat16)
+
+
+def test_chunked_forward_without_residual_matches_oracle():
+    d = case("6", 3, 80, 2, seed=41, starts=[[7, 8, 50], [0], [79]], lengths=[80, 48, 0], s0_scale=0.5)
+    t = dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    u = fam._expand_hn(t["u"], 2, 64, torch.bfloat16)
+    (s, y), _ = fam.batched_wkv6_fwd("6", t["r"], t["k"], t["v"], t["w"].reshape(t["r"].shape), u, t["s0"], length.cuda(), ns.cuda(), 3,
+                                     need_residual=False)
+    so, yo = oracle.wkv6_base_batched(*[t[n].double().cpu().numpy() for n in NAMES], d["length"], d["new_starts"], "6")
+    assert rel_err(npf(y), yo) < TOL[torch.bfloat16]
+    for i in range(3):
+        assert rel_err(npf(s[i]), so[i]) < TOL[torch.bfloat16]
