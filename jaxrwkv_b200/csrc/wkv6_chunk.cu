@@ -63,6 +63,22 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ uint32_t ld32(const bf* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
+// Sums each of eight per-lane values over the warp with nine shuffles: three halving steps leave one value per lane,
+// two butterflies finish.  Returns the total of v[which] with which = 4 bit4(lane) + 2 bit3(lane) + bit2(lane).
+__device__ __forceinline__ float warp_sum8(const float* v, int lane, int* which) {
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    float a[4], b[2], c;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a[j] = (b4 ? v[j + 4] : v[j]) + __shfl_xor_sync(0xffffffffu, b4 ? v[j] : v[j + 4], 16);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) b[j] = (b3 ? a[j + 2] : a[j]) + __shfl_xor_sync(0xffffffffu, b3 ? a[j] : a[j + 2], 8);
+    c = (b2 ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, b2 ? b[0] : b[1], 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    *which = (b4 ? 4 : 0) + (b3 ? 2 : 0) + (b2 ? 1 : 0);
+    return c;
+}
+
 // ------------------------------------------------------------------ forward ---------
 struct Fwd6cSmem {
     RawStage raw[kStages6];
@@ -214,16 +230,10 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             sm.kh[t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
             dsum[tt] = rv * uu * kv;
         }
-#pragma unroll
-        for (int tt = 0; tt < 8; ++tt) {
-#pragma unroll
-            for (int m = 1; m < 32; m <<= 1) dsum[tt] += __shfl_xor_sync(0xffffffffu, dsum[tt], m);
-        }
         {
-            float mine = 0.f;     // after the butterflies every lane holds every sum: lane tt keeps the one of token tt
-#pragma unroll
-            for (int tt = 0; tt < 8; ++tt) mine = lane == tt ? dsum[tt] : mine;
-            if (lane < 8) sm.dpart[warp & 1][8 * half + lane] = mine;
+            int which;
+            const float total = warp_sum8(dsum, lane, &which);
+            if (q == 0) sm.dpart[warp & 1][8 * half + which] = total;
         }
         __syncthreads();
 
@@ -305,14 +315,15 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 // token-by-channel results and 16 value rows of dS^T, and computes the 16x16 score blocks for itself.
 struct BwdStage {
     bf r[kC6][PITCH], k[kC6][PITCH], v[kC6][PITCH], w[kC6][PITCH], dy[kC6][PITCH];
-    bf s0[kN][PITCH];          // S0^T[j][i]
+    bf s0[kN][PITCH];          // S0^T[j][i]; once the products have read it, r dr' and k dk' per token and channel (fp32)
 };
+static_assert(sizeof(bf) * kN * PITCH >= 2 * sizeof(float) * kC6 * kN, "the two fp32 tiles must fit over the state tile");
 struct Bwd6cSmem {
     BwdStage st[2];
     bf ops[4][kC6][PITCH];     // R~, K~, R0, K^ while the products run; then dr, dk, dv, dw on their way out
     bf ds[kN][PITCH];          // dS_C^T[j][i] in bf16, for the one product that contracts over j
-    float c[kC6][kN];          // inclusive cumulative log-decay
-    float ea[kC6][kN], eb[kC6][kN];   // r dr' and k dk' per token and channel
+    float e2[kC6][kN], e3[kC6][kN];   // exp(c_{t-1} - c_m) and exp(c_m - c_t): what turns dR~, dK~ into dr, dk
+    float em[kN], ecm[kN];     // exp(c_m) and exp(c_C - c_m): the same for dR0 and dK^
     float tot[2][kN];
     float wc[kN];              // exp(c_C), or 0 when a start flag lies in the chunk
     float lump[kN];            // what every token of the chunk receives: the K^ references and the carried state
@@ -322,7 +333,7 @@ struct Bwd6cSmem {
     uint8_t ns[2][kC6];
 };
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ k, const bf* __restrict__ v,
                       const bf* __restrict__ w, int w_per_token, const bf* __restrict__ u,
                       const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
@@ -437,29 +448,29 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         {
             const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
             const float base = half ? c_m : 0.f;
-            if (half) sm.wc[ch] = seg_last == 0 ? __expf(c_C) : 0.f;
+            if (half) {
+                sm.wc[ch] = seg_last == 0 ? __expf(c_C) : 0.f;
+                sm.em[ch] = __expf(c_m);
+                sm.ecm[ch] = __expf(c_C - c_m);
+            }
             float dsum[8];
 #pragma unroll
             for (int tt = 0; tt < 8; ++tt) {
                 const int t = 8 * half + tt;
                 const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
                 const float rv = __bfloat162float(st.r[t][ch]), kv = __bfloat162float(st.k[t][ch]);
-                sm.c[t][ch] = c_t;
-                sm.ops[0][t][ch] = __float2bfloat16_rn(rv * __expf(fminf(c_prev - c_m, kMaxHalfDecay)));
-                sm.ops[1][t][ch] = __float2bfloat16_rn(kv * __expf(fminf(c_m - c_t, kMaxHalfDecay)));
+                const float f2 = __expf(fminf(c_prev - c_m, kMaxHalfDecay)), f3 = __expf(fminf(c_m - c_t, kMaxHalfDecay));
+                sm.e2[t][ch] = f2;
+                sm.e3[t][ch] = f3;
+                sm.ops[0][t][ch] = __float2bfloat16_rn(rv * f2);
+                sm.ops[1][t][ch] = __float2bfloat16_rn(kv * f3);
                 sm.ops[2][t][ch] = __float2bfloat16_rn(seg_mine[tt] == 0 ? rv * __expf(c_prev) : 0.f);
                 sm.ops[3][t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
                 dsum[tt] = rv * uu_a * kv;
             }
-#pragma unroll
-            for (int tt = 0; tt < 8; ++tt) {
-#pragma unroll
-                for (int m = 1; m < 32; m <<= 1) dsum[tt] += __shfl_xor_sync(0xffffffffu, dsum[tt], m);
-            }
-            float mine = 0.f;
-#pragma unroll
-            for (int tt = 0; tt < 8; ++tt) mine = lane == tt ? dsum[tt] : mine;
-            if (lane < 8) sm.dpart[warp & 1][8 * half + lane] = mine;
+            int which;
+            const float total = warp_sum8(dsum, lane, &which);
+            if (q == 0) sm.dpart[warp & 1][8 * half + which] = total;
         }
         __syncthreads();                                              // S3
         const bf (*Rt)[PITCH] = sm.ops[0];
@@ -587,39 +598,50 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             }
         }
         __syncthreads();                                              // S4: nobody reads the operand tiles any more
-        // ---- epilogue: rows t = g, g + 8; columns i = j0 + 8 nt + 2 q + (e & 1)
+        // ---- epilogue: rows t = g, g + 8; column pairs i = j0 + 8 nt + 2 q, + 1
+        float (*ea)[kN] = reinterpret_cast<float (*)[kN]>(sm.st[stage].s0);
+        float (*eb)[kN] = ea + kC6;
         {
-            float lump_part[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < 2; ++nt) {
+                const int i = j0 + 8 * nt + 2 * q;
+                const float2 em2 = *reinterpret_cast<const float2*>(&sm.em[i]), ecm2 = *reinterpret_cast<const float2*>(&sm.ecm[i]);
+                float lump0 = 0.f, lump1 = 0.f;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int t = g + 8 * (e >> 1), i = j0 + 8 * nt + 2 * q + (e & 1);
-                    const float c_t = sm.c[t][i], c_prev = t > 0 ? sm.c[t - 1][i] : 0.f, c_m = sm.c[7][i], c_C = sm.c[kC6 - 1][i];
-                    const float rv = __bfloat162float(st.r[t][i]), kv = __bfloat162float(st.k[t][i]);
-                    const float dd = (e >> 1) ? dd_hi : dd_lo, uc = u_col[nt][e & 1];
-                    const int sg = seg_r[e >> 1];
-                    const float drp = (sg == 0 ? dR0[nt][e] * __expf(c_prev) : 0.f) + dRt[nt][e] * __expf(fminf(c_prev - c_m, kMaxHalfDecay));
-                    const float kh_part = sg == seg_end ? dKh[nt][e] * __expf(c_C - c_t) : 0.f;
-                    const float dkp = dKt[nt][e] * __expf(fminf(c_m - c_t, kMaxHalfDecay)) + kh_part;
-                    sm.ops[0][t][i] = __float2bfloat16_rn(fmaf(dd * uc, kv, drp));
-                    sm.ops[1][t][i] = __float2bfloat16_rn(fmaf(dd * uc, rv, dkp));
-                    sm.ea[t][i] = rv * drp;
-                    sm.eb[t][i] = kv * dkp;
-                    lump_part[nt][e & 1] += kv * kh_part;
-                    du_acc[nt][e & 1] = fmaf(dd * rv, kv, du_acc[nt][e & 1]);
-                    sm.ops[2][t][i] = __float2bfloat16_rn(dV[nt][e]);      // dV: rows s = t, columns j = i (same index arithmetic)
+                for (int hh = 0; hh < 2; ++hh) {       // the two token rows
+                    const int t = g + 8 * hh, e0 = 2 * hh;
+                    const float2 f2 = *reinterpret_cast<const float2*>(&sm.e2[t][i]), f3 = *reinterpret_cast<const float2*>(&sm.e3[t][i]);
+                    const float2 rv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.r[t][i]));
+                    const float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.k[t][i]));
+                    const float dd = hh ? dd_hi : dd_lo;
+                    const int sg = seg_r[hh];
+                    const float m0 = sg == 0 ? 1.f : 0.f, mE = sg == seg_end ? 1.f : 0.f;
+                    // x: column i, y: column i + 1
+                    const float drp_x = (m0 * dR0[nt][e0] * em2.x + dRt[nt][e0]) * f2.x, drp_y = (m0 * dR0[nt][e0 + 1] * em2.y + dRt[nt][e0 + 1]) * f2.y;
+                    const float khp_x = mE * dKh[nt][e0] * ecm2.x * f3.x, khp_y = mE * dKh[nt][e0 + 1] * ecm2.y * f3.y;
+                    const float dkp_x = fmaf(dKt[nt][e0], f3.x, khp_x), dkp_y = fmaf(dKt[nt][e0 + 1], f3.y, khp_y);
+                    *reinterpret_cast<uint32_t*>(&sm.ops[0][t][i]) = pack2(fmaf(dd * u_col[nt][0], kv.x, drp_x), fmaf(dd * u_col[nt][1], kv.y, drp_y));
+                    *reinterpret_cast<uint32_t*>(&sm.ops[1][t][i]) = pack2(fmaf(dd * u_col[nt][0], rv.x, dkp_x), fmaf(dd * u_col[nt][1], rv.y, dkp_y));
+                    *reinterpret_cast<uint32_t*>(&sm.ops[2][t][i]) = pack2(dV[nt][e0], dV[nt][e0 + 1]);   // dV: rows s = t, columns j = i
+                    *reinterpret_cast<float2*>(&ea[t][i]) = make_float2(rv.x * drp_x, rv.y * drp_y);
+                    *reinterpret_cast<float2*>(&eb[t][i]) = make_float2(kv.x * dkp_x, kv.y * dkp_y);
+                    lump0 = fmaf(kv.x, khp_x, lump0);
+                    lump1 = fmaf(kv.y, khp_y, lump1);
+                    du_acc[nt][0] = fmaf(dd * rv.x, kv.x, du_acc[nt][0]);
+                    du_acc[nt][1] = fmaf(dd * rv.y, kv.y, du_acc[nt][1]);
                 }
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    float p = lump_part[nt][e];
-#pragma unroll
-                    for (int m = 4; m < 32; m <<= 1) p += __shfl_xor_sync(0xffffffffu, p, m);
-                    const int i = j0 + 8 * nt + 2 * q + e;
-                    if (g == 0) sm.lump[i] = p + (sm.gw[0][i] + sm.gw[1][i] + sm.gw[2][i] + sm.gw[3][i]) * sm.wc[i];
+                for (int m = 4; m < 32; m <<= 1) {
+                    lump0 += __shfl_xor_sync(0xffffffffu, lump0, m);
+                    lump1 += __shfl_xor_sync(0xffffffffu, lump1, m);
                 }
+                if (g == 0) {
+                    const float2 wc2 = *reinterpret_cast<const float2*>(&sm.wc[i]);
+                    const float gx = sm.gw[0][i] + sm.gw[1][i] + sm.gw[2][i] + sm.gw[3][i];
+                    const float gy = sm.gw[0][i + 1] + sm.gw[1][i + 1] + sm.gw[2][i + 1] + sm.gw[3][i + 1];
+                    *reinterpret_cast<float2*>(&sm.lump[i]) = make_float2(fmaf(gx, wc2.x, lump0), fmaf(gy, wc2.y, lump1));
+                }
+            }
         }
         __syncthreads();                                              // S5
         if (tid < kN) {
@@ -627,7 +649,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             float run2 = sm.lump[tid];
 #pragma unroll
             for (int x = kC6 - 1; x >= 0; --x) {
-                run2 += (x + 1 < kC6 ? sm.ea[x + 1][tid] : 0.f) - sm.eb[x][tid];
+                run2 += (x + 1 < kC6 ? ea[x + 1][tid] : 0.f) - eb[x][tid];
                 if (w_per_token) sm.ops[3][x][tid] = __float2bfloat16_rn(run2);
                 else if (t0 + x < Tlen) dw_acc += run2;
             }
