@@ -211,7 +211,11 @@ int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int 
     if (residual != nullptr && residual_bytes < b200wkv6_residual_bytes(dtype, B, T, H, N)) return B200WKV_ERESIDUAL;
     if (dtype == B200WKV_BF16) {
         int* mark = residual_mark_of(residual, b200wkv6_residual_bytes(dtype, B, T, H, N));
-        if (flags & B200WKV_FLAG_SEQUENTIAL)
+        // With a constant decay (versions 5, 5.2) the decay's gradient is a sum over ALL tokens of per-token terms that
+        // largely cancel; taken from bf16 tensor-core products it is only good to a few percent (10 % on short
+        // sequences), so training calls of those versions keep the fp32-arithmetic sequential kernels.  Their
+        // inference calls, and everything of version 6, take the chunked kernels.
+        if ((flags & B200WKV_FLAG_SEQUENTIAL) || (version != 6 && residual != nullptr))
             return wkv6_seq_fwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, s0, length, new_starts, y,
                                 s_out, residual, nullptr, 0, mark);
         // the chunked tensor-core kernel, and behind it the sequential kernel, which runs only if the chunked one met

@@ -14,10 +14,12 @@
 // layout of a right operand, so nothing but the scaled operands passes through shared memory.  The chunk is 16
 // tokens because the per-channel decay is unbounded: referenced to the chunk's middle the scaling factors stay
 // below exp(8 |lw|), which fp32 / bf16 hold for |lw| <= 10 per token (decay >= 4.5e-5); a chunk beyond that, or a
-// `length` that is not a chunk boundary, makes the kernel leave its ticket in a flag and the token-sequential
-// kernels (wkv6_seq.cu) redo the call.  tcgen05 does not apply: its smallest tile is 64 tokens.
+// decay above 1, makes the kernel leave its ticket in a flag and the token-sequential kernels (wkv6_seq.cu) redo the
+// call.  A `length` inside a chunk splits that chunk in two parts that are walked like two chunks.  tcgen05 does not apply: its smallest tile is 64 tokens.
 //
 // Semantics: BaseRWKV.inner_loop of jaxrwkv, src/jaxrwkv/rwkv6.py:174-191, rwkv5_2.py:164-180, rwkv5.py:161-177.
+#include <type_traits>
+
 #include "common.cuh"
 #include "device_once.cuh"
 
@@ -92,9 +94,9 @@ struct Fwd6cSmem {
 };
 
 // One CTA of 128 threads per (batch, head).  ckpt: the state entering every chunk, bf16 [value j][key i], for
-// the backward (may be NULL).  The kernel gives up (flag := ticket, see the file header) on a length that is not
-// a chunk boundary and on a half-chunk decay beyond exp(-80).
-__global__ void __launch_bounds__(128)
+// the backward (may be NULL).  The kernel gives up (flag := ticket, see the file header) on a decay above 1 and on a
+// half-chunk decay beyond exp(-80).
+__global__ void __launch_bounds__(128, 4)
 wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ k, const bf* __restrict__ v,
                       const bf* __restrict__ w, int w_per_token, const bf* __restrict__ u, const bf* __restrict__ s0,
                       const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts, bf* __restrict__ y,
@@ -112,11 +114,11 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     const int L = min((int)length[bi], Tlen);
     const int nC = (Tlen + kC6 - 1) / kC6;
     if (bh == 0 && tid == 0 && residual_mark != nullptr) *residual_mark = 0;   // chunked format (so far)
-    if (L % kC6 != 0 && L != Tlen) {
-        if (tid == 0) atomicExch(flag, ticket);
-        return;
-    }
-    const int c_out = L > 0 ? (L - 1) / kC6 : -1;                // the returned state leaves this chunk
+    const int c_out = L > 0 ? (L - 1) / kC6 : -1;                // the returned state leaves this chunk ...
+    const int p_out = L > 0 ? (L - 1) % kC6 : -1;                // ... behind this token of it
+    // A length inside a chunk: that chunk is walked in two parts, tokens 0..p_out and the rest, as if they were
+    // two chunks (tokens outside the part at hand are inert: no decay, zero r and k, no output).
+    const bool split = L > 0 && L < Tlen && p_out != kC6 - 1;
 
     // S^T tiles: acc[ni][e] = S[i = 8 ni + 2 q + (e & 1)][j = j0 + g + 8 (e >> 1)]
     float acc[8][4];
@@ -166,21 +168,30 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
     bool bad = false;
 
-    for (int c = 0; c < nC; ++c) {
-        cp_async_wait<1>();
-        __syncthreads();          // chunk c has landed for everyone; the tiles of chunk c - 1 are no longer read
-        issue(c + 2);
-        if (tid < kC6) sm.ns[(c + 2) % kStages6][tid] = ns_ahead;
-        ns_ahead = load_ns(c + 3);
+    // One chunk, or one part of the split chunk.  The two cases are separate instantiations: in the common one the
+    // bounds of the part are the constants 0 and 16 and every test against them folds away.
+    auto walk = [&](auto split_tag, const int c, const int part_arg) {
+        constexpr bool kSplitHere = decltype(split_tag)::value;
+        const int part = kSplitHere ? part_arg : 0;
+        const int lo = (kSplitHere && part == 1) ? p_out + 1 : 0, hi = (kSplitHere && part == 0) ? p_out + 1 : kC6;
         const RawStage& st = sm.raw[c % kStages6];
         const int t0 = c * kC6;
-        // ---- outputs of the previous chunk to global memory
-        if (c > 0 && t0 - kC6 + srow < Tlen)
-            *reinterpret_cast<uint4*>(y + seq_base + (size_t)(t0 - kC6 + srow) * tok_stride + spiece) =
-                *reinterpret_cast<const uint4*>(&sm.ys[srow][spiece]);
-        // ---- the entering state for the backward
+        if (part == 0) {
+            cp_async_wait<1>();
+            __syncthreads();          // chunk c has landed for everyone; the tiles of chunk c - 1 are no longer read
+            issue(c + 2);
+            if (tid < kC6) sm.ns[(c + 2) % kStages6][tid] = ns_ahead;
+            ns_ahead = load_ns(c + 3);
+            // ---- outputs of the previous chunk to global memory
+            if (c > 0 && t0 - kC6 + srow < Tlen)
+                *reinterpret_cast<uint4*>(y + seq_base + (size_t)(t0 - kC6 + srow) * tok_stride + spiece) =
+                    *reinterpret_cast<const uint4*>(&sm.ys[srow][spiece]);
+        } else {
+            __syncthreads();          // the first part's products have read the operand tiles
+        }
+        // ---- the entering state for the backward (of the second part of a split chunk: slot nC)
         if (ckpt != nullptr) {
-            bf* dst = ckpt + ((size_t)bh * nC + c) * kN * kN;
+            bf* dst = ckpt + ((size_t)bh * (nC + 1) + (part == 0 ? c : nC)) * kN * kN;
 #pragma unroll
             for (int ni = 0; ni < 8; ++ni) {
                 *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g) * kN + 8 * ni + 2 * q) = pack2(acc[ni][0], acc[ni][1]);
@@ -188,23 +199,24 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             }
         }
         // ---- phase A: cumulative log-decay and scaled operands
-        int seg_mine[8], seg_last;
+        int seg_mine[8], seg_last = 0, seg_base = 0;      // segment of the part's last token; of the state entering the part
         {
             int cnt = 0;
 #pragma unroll
             for (int t = 0; t < kC6; ++t) {
+                if (t == lo) seg_base = cnt;
                 cnt += sm.ns[c % kStages6][t] != 0;
                 if ((t >> 3) == half) seg_mine[t & 7] = cnt;      // resolved at compile time per unrolled t, selected by half
                 if (tid == t) sm.seg[t] = cnt;
+                if (t == hi - 1) seg_last = cnt;
             }
-            seg_last = cnt;
         }
         float lw[8], cl[8];
         float run = 0.f;
 #pragma unroll
         for (int tt = 0; tt < 8; ++tt) {
             const int t = 8 * half + tt;
-            const bool ok = t0 + t < Tlen;
+            const bool ok = t0 + t < Tlen && t >= lo && t < hi;
             lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
             if (!(lw[tt] <= 0.f)) bad = true;      // a decay above 1 (or NaN) is outside what the scaling covers
             run += lw[tt];
@@ -217,16 +229,17 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         if (fabsf(tot0) > kMaxHalfDecay || fabsf(tot1) > kMaxHalfDecay) bad = true;
         const float c_m = fmaxf(tot0, -kMaxHalfDecay), c_C = c_m + fmaxf(tot1, -kMaxHalfDecay);
         const float base = half ? c_m : 0.f;
-        if (half) sm.wc[ch] = seg_last == 0 ? __expf(c_C) : 0.f;
+        if (half) sm.wc[ch] = seg_last == seg_base ? __expf(c_C) : 0.f;
         float dsum[8];
 #pragma unroll
         for (int tt = 0; tt < 8; ++tt) {
             const int t = 8 * half + tt;
+            const bool in_part = t >= lo && t < hi;
             const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
-            const float rv = __bfloat162float(st.r[t][ch]), kv = __bfloat162float(st.k[t][ch]);
+            const float rv = in_part ? __bfloat162float(st.r[t][ch]) : 0.f, kv = in_part ? __bfloat162float(st.k[t][ch]) : 0.f;
             sm.rt[t][ch] = __float2bfloat16_rn(rv * __expf(fminf(c_prev - c_m, kMaxHalfDecay)));
             sm.kt[t][ch] = __float2bfloat16_rn(kv * __expf(fminf(c_m - c_t, kMaxHalfDecay)));
-            sm.r0[t][ch] = __float2bfloat16_rn(seg_mine[tt] == 0 ? rv * __expf(c_prev) : 0.f);
+            sm.r0[t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_base ? rv * __expf(c_prev) : 0.f);
             sm.kh[t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
             dsum[tt] = rv * uu * kv;
         }
@@ -265,7 +278,7 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int t = g + 8 * (e >> 1), s = 8 * nt + 2 * q + (e & 1);
-                const bool keep = s < t && sm.seg[s] == sm.seg[t];
+                const bool keep = s < t && sm.seg[s] == sm.seg[t];      // (rows and columns outside the part are zero operands)
                 sacc[nt][e] = keep ? sacc[nt][e] : (s == t ? sm.dpart[0][t] + sm.dpart[1][t] : 0.f);
             }
         // Y^T += V^T A^T: the score tiles are the right operand as they are
@@ -274,7 +287,10 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) sm.ys[8 * nt + 2 * q + (e & 1)][j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(yacc[nt][e]);
+            for (int e = 0; e < 4; ++e) {
+                const int t = 8 * nt + 2 * q + (e & 1);
+                if (t >= lo && t < hi) sm.ys[t][j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(yacc[nt][e]);
+            }
         // S^T <- S^T diag(exp(c_C)) [no start in the chunk] + V^T K^
         {
             const int mi = lane >> 3, r8 = lane & 7;
@@ -290,7 +306,15 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
                 mma_bf16(acc[2 * np + 1], va[0], va[1], va[2], va[3], b2, b3);
             }
         }
-        if (c == c_out) write_state(s_out);
+        if (c == c_out && part == 0) write_state(s_out);
+    };
+    for (int c = 0; c < nC; ++c) {
+        if (split && c == c_out) {
+#pragma unroll 1
+            for (int part = 0; part < 2; ++part) walk(std::true_type{}, c, part);
+        } else {
+            walk(std::false_type{}, c, 0);
+        }
     }
     __syncthreads();
     {
@@ -352,7 +376,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     const size_t st_base = (size_t)bh * kN * kN;
     const int L = min((int)length[bi], Tlen);
     const int nC = (Tlen + kC6 - 1) / kC6;
-    const int c_out = L > 0 ? (L - 1) / kC6 : -1;
+    const int c_out = L > 0 ? (L - 1) / kC6 : -1, p_out = L > 0 ? (L - 1) % kC6 : -1;
+    const bool split = L > 0 && L < Tlen && p_out != kC6 - 1;      // see the forward: that chunk is walked in two parts
 
     float acc[8][4];
 #pragma unroll
@@ -380,11 +405,21 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             cp_async16_zfill(&st.v[srow][spiece], v + off, ok);
             if (w_per_token) cp_async16_zfill(&st.w[srow][spiece], w + off, ok);
             cp_async16_zfill(&st.dy[srow][spiece], dy != nullptr ? dy + off : r + off, ok && dy != nullptr);
-            const bf* src = ckpt + ((size_t)bh * nC + c) * kN * kN;
+            const bf* src = ckpt + ((size_t)bh * (nC + 1) + c) * kN * kN;
 #pragma unroll
             for (int rr = 0; rr < 4; ++rr) cp_async16_zfill(&st.s0[srow + 16 * rr][spiece], src + (size_t)(srow + 16 * rr) * kN + spiece, true);
         }
         cp_async_commit();
+    };
+    // the state entering a part of the split chunk, fetched on the spot (once or twice per sequence)
+    auto fetch_state = [&](int slot, int stage) {
+        const bf* src = ckpt + ((size_t)bh * (nC + 1) + slot) * kN * kN;
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr)
+            cp_async16_zfill(&sm.st[stage].s0[srow + 16 * rr][spiece], src + (size_t)(srow + 16 * rr) * kN + spiece, true);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
     };
     auto load_ns = [&](int c) -> uint8_t {
         const int t = c * kC6 + tid;
@@ -405,16 +440,25 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     float du_acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     float dw_acc = 0.f;                        // constant decay: sum over tokens of the log-decay gradient (thread ch < 64)
 
-    for (int c = nC - 1, it = 0; c >= 0; --c, ++it) {
+    auto walk = [&](auto split_tag, const int c, const int it, const int part_arg) {
+        constexpr bool kSplitHere = decltype(split_tag)::value;
+        const bool split_here = kSplitHere;
+        const int part = kSplitHere ? part_arg : 0;
         const int stage = it & 1;
-        cp_async_wait<0>();
-        __syncthreads();                                              // S1
-        issue(c - 1, stage ^ 1);
-        if (tid < kC6) sm.ns[stage ^ 1][tid] = ns_ahead;
-        ns_ahead = load_ns(c - 2);
+        const int lo = (kSplitHere && part == 1) ? p_out + 1 : 0, hi = (kSplitHere && part == 0) ? p_out + 1 : kC6;
+        if (!split_here || part == 1) {                               // first visit of the chunk
+            cp_async_wait<0>();
+            __syncthreads();                                          // S1
+            issue(c - 1, stage ^ 1);
+            if (tid < kC6) sm.ns[stage ^ 1][tid] = ns_ahead;
+            ns_ahead = load_ns(c - 2);
+            if (split_here) fetch_state(nC, stage);                   // the state behind token p_out
+        } else {
+            fetch_state(c, stage);                                    // (its barrier also retires the first visit's reads)
+        }
         const BwdStage& st = sm.st[stage];
         const int t0 = c * kC6;
-        if (c == c_out) add_ds_out();
+        if (c == c_out && part == 0) add_ds_out();
         // dS_C^T in bf16 for the product that contracts over value rows
 #pragma unroll
         for (int ni = 0; ni < 8; ++ni) {
@@ -422,23 +466,24 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             *reinterpret_cast<uint32_t*>(&sm.ds[j0 + g + 8][8 * ni + 2 * q]) = pack2(acc[ni][2], acc[ni][3]);
         }
         // ---- phase A: as in the forward
-        int seg_mine[8], seg_last;
+        int seg_mine[8], seg_last = 0, seg_base = 0;
         {
             int cnt = 0;
 #pragma unroll
             for (int t = 0; t < kC6; ++t) {
+                if (t == lo) seg_base = cnt;
                 cnt += sm.ns[stage][t] != 0;
                 if ((t >> 3) == half) seg_mine[t & 7] = cnt;
                 if (tid == t) sm.seg[t] = cnt;
+                if (t == hi - 1) seg_last = cnt;
             }
-            seg_last = cnt;
         }
         float lw[8], cl[8];
         float run = 0.f;
 #pragma unroll
         for (int tt = 0; tt < 8; ++tt) {
             const int t = 8 * half + tt;
-            const bool ok = t0 + t < Tlen;
+            const bool ok = t0 + t < Tlen && t >= lo && t < hi;
             lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
             run += lw[tt];
             cl[tt] = run;
@@ -449,7 +494,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
             const float base = half ? c_m : 0.f;
             if (half) {
-                sm.wc[ch] = seg_last == 0 ? __expf(c_C) : 0.f;
+                sm.wc[ch] = seg_last == seg_base ? __expf(c_C) : 0.f;
                 sm.em[ch] = __expf(c_m);
                 sm.ecm[ch] = __expf(c_C - c_m);
             }
@@ -458,13 +503,14 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             for (int tt = 0; tt < 8; ++tt) {
                 const int t = 8 * half + tt;
                 const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
-                const float rv = __bfloat162float(st.r[t][ch]), kv = __bfloat162float(st.k[t][ch]);
+                const bool in_part = t >= lo && t < hi;
+                const float rv = in_part ? __bfloat162float(st.r[t][ch]) : 0.f, kv = in_part ? __bfloat162float(st.k[t][ch]) : 0.f;
                 const float f2 = __expf(fminf(c_prev - c_m, kMaxHalfDecay)), f3 = __expf(fminf(c_m - c_t, kMaxHalfDecay));
                 sm.e2[t][ch] = f2;
                 sm.e3[t][ch] = f3;
                 sm.ops[0][t][ch] = __float2bfloat16_rn(rv * f2);
                 sm.ops[1][t][ch] = __float2bfloat16_rn(kv * f3);
-                sm.ops[2][t][ch] = __float2bfloat16_rn(seg_mine[tt] == 0 ? rv * __expf(c_prev) : 0.f);
+                sm.ops[2][t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_base ? rv * __expf(c_prev) : 0.f);
                 sm.ops[3][t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
                 dsum[tt] = rv * uu_a * kv;
             }
@@ -513,13 +559,14 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             dd_hi = __shfl_sync(0xffffffffu, cand_hi, src);
         }
         int seg_r[2] = {sm.seg[g], sm.seg[g + 8]};
-        const int seg_end = sm.seg[kC6 - 1];
+        const int seg_end = sm.seg[hi - 1], seg_in = lo > 0 ? sm.seg[lo - 1] : 0;     // as seg_last / seg_base of phase A
+        const bool row_in[2] = {g >= lo && g < hi, g + 8 >= lo && g + 8 < hi};
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int row = g + 8 * (e >> 1), col = 8 * nt + 2 * q + (e & 1);
-                const bool same = sm.seg[col] == seg_r[e >> 1];
+                const bool same = sm.seg[col] == seg_r[e >> 1] && row_in[e >> 1] && col >= lo && col < hi;
                 dA[nt][e] = (col < row && same) ? dA[nt][e] : 0.f;                       // rows t, columns s < t
                 dAT[nt][e] = (row < col && same) ? dAT[nt][e] : 0.f;                     // rows s, columns t > s
                 AT[nt][e] = (row < col && same) ? AT[nt][e] : (row == col ? sm.dpart[0][row] + sm.dpart[1][row] : 0.f);
@@ -615,7 +662,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
                     const float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.k[t][i]));
                     const float dd = hh ? dd_hi : dd_lo;
                     const int sg = seg_r[hh];
-                    const float m0 = sg == 0 ? 1.f : 0.f, mE = sg == seg_end ? 1.f : 0.f;
+                    const float live = row_in[hh] ? 1.f : 0.f;
+                    const float m0 = sg == seg_in ? live : 0.f, mE = sg == seg_end ? live : 0.f;
                     // x: column i, y: column i + 1
                     const float drp_x = (m0 * dR0[nt][e0] * em2.x + dRt[nt][e0]) * f2.x, drp_y = (m0 * dR0[nt][e0 + 1] * em2.y + dRt[nt][e0 + 1]) * f2.y;
                     const float khp_x = mE * dKh[nt][e0] * ecm2.x * f3.x, khp_y = mE * dKh[nt][e0 + 1] * ecm2.y * f3.y;
@@ -627,8 +675,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
                     *reinterpret_cast<float2*>(&eb[t][i]) = make_float2(kv.x * dkp_x, kv.y * dkp_y);
                     lump0 = fmaf(kv.x, khp_x, lump0);
                     lump1 = fmaf(kv.y, khp_y, lump1);
-                    du_acc[nt][0] = fmaf(dd * rv.x, kv.x, du_acc[nt][0]);
-                    du_acc[nt][1] = fmaf(dd * rv.y, kv.y, du_acc[nt][1]);
+                    du_acc[nt][0] = fmaf(live * dd * rv.x, kv.x, du_acc[nt][0]);
+                    du_acc[nt][1] = fmaf(live * dd * rv.y, kv.y, du_acc[nt][1]);
                 }
 #pragma unroll
                 for (int m = 4; m < 32; m <<= 1) {
@@ -651,19 +699,27 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             for (int x = kC6 - 1; x >= 0; --x) {
                 run2 += (x + 1 < kC6 ? ea[x + 1][tid] : 0.f) - eb[x][tid];
                 if (w_per_token) sm.ops[3][x][tid] = __float2bfloat16_rn(run2);
-                else if (t0 + x < Tlen) dw_acc += run2;
+                else if (t0 + x < Tlen && x >= lo && x < hi) dw_acc += run2;
             }
         }
         __syncthreads();                                              // S6
         {
             const int t = t0 + srow;
-            if (t < Tlen) {
+            if (t < Tlen && srow >= lo && srow < hi) {
                 const size_t off = seq_base + (size_t)t * tok_stride + spiece;
                 *reinterpret_cast<uint4*>(dr + off) = *reinterpret_cast<const uint4*>(&sm.ops[0][srow][spiece]);
                 *reinterpret_cast<uint4*>(dk + off) = *reinterpret_cast<const uint4*>(&sm.ops[1][srow][spiece]);
                 *reinterpret_cast<uint4*>(dv + off) = *reinterpret_cast<const uint4*>(&sm.ops[2][srow][spiece]);
                 if (w_per_token) *reinterpret_cast<uint4*>(dw_tok + off) = *reinterpret_cast<const uint4*>(&sm.ops[3][srow][spiece]);
             }
+        }
+    };
+    for (int c = nC - 1, it = 0; c >= 0; --c, ++it) {
+        if (split && c == c_out) {
+#pragma unroll 1
+            for (int part = 1; part >= 0; --part) walk(std::true_type{}, c, it, part);   // tokens behind `length` first
+        } else {
+            walk(std::false_type{}, c, it, 0);
         }
     }
     if (L == 0) add_ds_out();
@@ -688,7 +744,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 }  // namespace
 
 size_t wkv6_chunk_residual_bytes(int B, int T, int H) {
-    return (size_t)B * H * ((T + kC6 - 1) / kC6) * kN * kN * sizeof(bf);
+    return (size_t)B * H * ((T + kC6 - 1) / kC6 + 1) * kN * kN * sizeof(bf);   // every chunk, and the second part of a split one
 }
 
 int wkv6_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
