@@ -53,6 +53,28 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"((uint32_t)__cvta_generic_to_shared(row)));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
+// One 16-token x 16-channel block of a row-major [token][channel] tile, f[0..3] = (tokens 0-7 | 8-15) x (channels 0-7 |
+// 8-15) in the order (0-7, 0-7), (8-15, 0-7), (0-7, 8-15), (8-15, 8-15).  As a LEFT operand (rows = tokens) the four
+// are a0..a3; as a RIGHT operand (n = token, k = channel) tokens 0-7 take (f[0], f[2]) and tokens 8-15 (f[1], f[3]).
+struct Frag {
+    uint32_t f[4];
+};
+__device__ __forceinline__ Frag load_frag(const bf (*tile)[72], int ks, int lane) {
+    Frag x;
+    const int mi = lane >> 3, r8 = lane & 7;
+    ldmatrix_x4(x.f[0], x.f[1], x.f[2], x.f[3], &tile[(mi & 1) * 8 + r8][16 * ks + (mi >> 1) * 8]);
+    return x;
+}
+__device__ __forceinline__ void mma_ab(float* d, const Frag& a, const Frag& b, int nt) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a.f[0]), "r"(a.f[1]), "r"(a.f[2]), "r"(a.f[3]), "r"(b.f[nt]), "r"(b.f[nt + 2]));
+}
 // D(16x8, fp32) += A(16x16, bf16, row) B(16x8, bf16, col)
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -90,6 +112,7 @@ struct Fwd6cSmem {
     float wc[kN];            // exp(c_C), or 0 when a start flag lies in the chunk
     float dpart[2][kC6];     // sum_i r u k per token, one partial per 32 channels
     int seg[kC6];            // number of start flags at or before the token, inside the chunk
+    unsigned startmask;      // bit t: start flag on token t of the chunk
     uint8_t ns[kStages6][kC6];
 };
 
@@ -199,17 +222,9 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             }
         }
         // ---- phase A: cumulative log-decay and scaled operands
-        int seg_mine[8], seg_last = 0, seg_base = 0;      // segment of the part's last token; of the state entering the part
-        {
-            int cnt = 0;
-#pragma unroll
-            for (int t = 0; t < kC6; ++t) {
-                if (t == lo) seg_base = cnt;
-                cnt += sm.ns[c % kStages6][t] != 0;
-                if ((t >> 3) == half) seg_mine[t & 7] = cnt;      // resolved at compile time per unrolled t, selected by half
-                if (tid == t) sm.seg[t] = cnt;
-                if (t == hi - 1) seg_last = cnt;
-            }
+        if (warp == 0) {
+            const unsigned m = __ballot_sync(0xffffffffu, lane < kC6 && sm.ns[c % kStages6][lane] != 0);
+            if (lane == 0) sm.startmask = m;
         }
         float lw[8], cl[8];
         float run = 0.f;
@@ -225,6 +240,14 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         sm.tot[half][ch] = run;
         // the operands need the other half's total: a barrier of the whole CTA
         __syncthreads();
+        // segments: seg(t) = number of start flags at or before token t
+        const unsigned starts = sm.startmask;
+        auto seg_of = [&](int t) { return __popc(starts & ((2u << t) - 1u)); };
+        const int seg_last = seg_of(hi - 1), seg_base = lo > 0 ? seg_of(lo - 1) : 0;   // of the part's last token; of the state entering it
+        int seg_mine[8];
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) seg_mine[tt] = seg_of(8 * half + tt);
+        if (tid < kC6) sm.seg[tid] = seg_of(tid);
         const float tot0 = sm.tot[0][ch], tot1 = sm.tot[1][ch];
         if (fabsf(tot0) > kMaxHalfDecay || fabsf(tot1) > kMaxHalfDecay) bad = true;
         const float c_m = fmaxf(tot0, -kMaxHalfDecay), c_C = c_m + fmaxf(tot1, -kMaxHalfDecay);
@@ -262,14 +285,11 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         for (int ks = 0; ks < 4; ++ks) {
             const uint32_t s_a0 = pack2(acc[2 * ks][0], acc[2 * ks][1]), s_a1 = pack2(acc[2 * ks][2], acc[2 * ks][3]);
             const uint32_t s_a2 = pack2(acc[2 * ks + 1][0], acc[2 * ks + 1][1]), s_a3 = pack2(acc[2 * ks + 1][2], acc[2 * ks + 1][3]);
-            const uint32_t r_a0 = ld32(&sm.rt[g][16 * ks + 2 * q]), r_a1 = ld32(&sm.rt[g + 8][16 * ks + 2 * q]);
-            const uint32_t r_a2 = ld32(&sm.rt[g][16 * ks + 8 + 2 * q]), r_a3 = ld32(&sm.rt[g + 8][16 * ks + 8 + 2 * q]);
+            const Frag fr = load_frag(sm.rt, ks, lane), f0 = load_frag(sm.r0, ks, lane), fk = load_frag(sm.kt, ks, lane);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                mma_bf16(yacc[nt], s_a0, s_a1, s_a2, s_a3, ld32(&sm.r0[8 * nt + g][16 * ks + 2 * q]),
-                         ld32(&sm.r0[8 * nt + g][16 * ks + 8 + 2 * q]));
-                mma_bf16(sacc[nt], r_a0, r_a1, r_a2, r_a3, ld32(&sm.kt[8 * nt + g][16 * ks + 2 * q]),
-                         ld32(&sm.kt[8 * nt + g][16 * ks + 8 + 2 * q]));
+                mma_bf16(yacc[nt], s_a0, s_a1, s_a2, s_a3, f0.f[nt], f0.f[nt + 2]);
+                mma_ab(sacc[nt], fr, fk, nt);
             }
         }
         // masks: strictly earlier tokens of the same segment; the diagonal is the u term
@@ -354,6 +374,7 @@ struct Bwd6cSmem {
     float gw[4][kN];           // sum_j dS_C S0 over each warp's value rows
     float dpart[2][kC6];
     int seg[kC6];
+    unsigned startmask;
     uint8_t ns[2][kC6];
 };
 
@@ -466,17 +487,9 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             *reinterpret_cast<uint32_t*>(&sm.ds[j0 + g + 8][8 * ni + 2 * q]) = pack2(acc[ni][2], acc[ni][3]);
         }
         // ---- phase A: as in the forward
-        int seg_mine[8], seg_last = 0, seg_base = 0;
-        {
-            int cnt = 0;
-#pragma unroll
-            for (int t = 0; t < kC6; ++t) {
-                if (t == lo) seg_base = cnt;
-                cnt += sm.ns[stage][t] != 0;
-                if ((t >> 3) == half) seg_mine[t & 7] = cnt;
-                if (tid == t) sm.seg[t] = cnt;
-                if (t == hi - 1) seg_last = cnt;
-            }
+        if (warp == 0) {
+            const unsigned m = __ballot_sync(0xffffffffu, lane < kC6 && sm.ns[stage][lane] != 0);
+            if (lane == 0) sm.startmask = m;
         }
         float lw[8], cl[8];
         float run = 0.f;
@@ -491,6 +504,13 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         sm.tot[half][ch] = run;
         __syncthreads();                                              // S2
         {
+            const unsigned starts = sm.startmask;
+            auto seg_of = [&](int t) { return __popc(starts & ((2u << t) - 1u)); };
+            const int seg_last = seg_of(hi - 1), seg_base = lo > 0 ? seg_of(lo - 1) : 0;
+            int seg_mine[8];
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) seg_mine[tt] = seg_of(8 * half + tt);
+            if (tid < kC6) sm.seg[tid] = seg_of(tid);
             const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
             const float base = half ? c_m : 0.f;
             if (half) {
@@ -527,27 +547,17 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         // ---- the 16x16 blocks: dA (t x s), dA^T (s x t), A^T (s x t)
         float dA[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dAT[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         float AT[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        uint32_t dya[4][4], vaf[4][4];        // dY and V as left operands (rows token, K = value j), all four K steps
+        Frag fdy[4], fv[4];                   // dY and V, all four K steps (left and right operands alike)
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-            dya[ks][0] = ld32(&st.dy[g][16 * ks + 2 * q]);      dya[ks][1] = ld32(&st.dy[g + 8][16 * ks + 2 * q]);
-            dya[ks][2] = ld32(&st.dy[g][16 * ks + 8 + 2 * q]);  dya[ks][3] = ld32(&st.dy[g + 8][16 * ks + 8 + 2 * q]);
-            vaf[ks][0] = ld32(&st.v[g][16 * ks + 2 * q]);       vaf[ks][1] = ld32(&st.v[g + 8][16 * ks + 2 * q]);
-            vaf[ks][2] = ld32(&st.v[g][16 * ks + 8 + 2 * q]);   vaf[ks][3] = ld32(&st.v[g + 8][16 * ks + 8 + 2 * q]);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t k_a0 = ld32(&Kt[g][16 * ks + 2 * q]), k_a1 = ld32(&Kt[g + 8][16 * ks + 2 * q]);
-            const uint32_t k_a2 = ld32(&Kt[g][16 * ks + 8 + 2 * q]), k_a3 = ld32(&Kt[g + 8][16 * ks + 8 + 2 * q]);
+            fdy[ks] = load_frag(st.dy, ks, lane);
+            fv[ks] = load_frag(st.v, ks, lane);
+            const Frag fk = load_frag(Kt, ks, lane), fr = load_frag(Rt, ks, lane);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                // as right operands a row-major [token][channel] tile is read along its rows: n = token, k = channel
-                mma_bf16(dA[nt], dya[ks][0], dya[ks][1], dya[ks][2], dya[ks][3], ld32(&st.v[8 * nt + g][16 * ks + 2 * q]),
-                         ld32(&st.v[8 * nt + g][16 * ks + 8 + 2 * q]));
-                mma_bf16(dAT[nt], vaf[ks][0], vaf[ks][1], vaf[ks][2], vaf[ks][3], ld32(&st.dy[8 * nt + g][16 * ks + 2 * q]),
-                         ld32(&st.dy[8 * nt + g][16 * ks + 8 + 2 * q]));
-                mma_bf16(AT[nt], k_a0, k_a1, k_a2, k_a3, ld32(&Rt[8 * nt + g][16 * ks + 2 * q]),
-                         ld32(&Rt[8 * nt + g][16 * ks + 8 + 2 * q]));
+                mma_ab(dA[nt], fdy[ks], fv[ks], nt);
+                mma_ab(dAT[nt], fv[ks], fdy[ks], nt);
+                mma_ab(AT[nt], fk, fr, nt);
             }
         }
         // dd of this thread's two token rows: the diagonal of dA sits in lane 4 g + g / 2
@@ -582,8 +592,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             mma_bf16(dV[1], a0, a1, a2, a3, b2, b3);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                const uint32_t h0 = ld32(&Kh[g][16 * ks + 2 * q]), h1 = ld32(&Kh[g + 8][16 * ks + 2 * q]);
-                const uint32_t h2 = ld32(&Kh[g][16 * ks + 8 + 2 * q]), h3 = ld32(&Kh[g + 8][16 * ks + 8 + 2 * q]);
+                const Frag fh = load_frag(Kh, ks, lane);
+                const uint32_t h0 = fh.f[0], h1 = fh.f[1], h2 = fh.f[2], h3 = fh.f[3];
                 // dS_C^T tiles as right operand: K = key channel (their columns), n = value row (their rows)
                 mma_bf16(dV[0], h0, h1, h2, h3, pack2(acc[2 * ks][0], acc[2 * ks][1]), pack2(acc[2 * ks + 1][0], acc[2 * ks + 1][1]));
                 mma_bf16(dV[1], h0, h1, h2, h3, pack2(acc[2 * ks][2], acc[2 * ks][3]), pack2(acc[2 * ks + 1][2], acc[2 * ks + 1][3]));
@@ -596,11 +606,11 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         for (int ks = 0; ks < 4; ++ks) {
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4_trans(b0, b1, b2, b3, &st.s0[16 * ks + (mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
-            mma_bf16(dR0[0], dya[ks][0], dya[ks][1], dya[ks][2], dya[ks][3], b0, b1);
-            mma_bf16(dR0[1], dya[ks][0], dya[ks][1], dya[ks][2], dya[ks][3], b2, b3);
+            mma_bf16(dR0[0], fdy[ks].f[0], fdy[ks].f[1], fdy[ks].f[2], fdy[ks].f[3], b0, b1);
+            mma_bf16(dR0[1], fdy[ks].f[0], fdy[ks].f[1], fdy[ks].f[2], fdy[ks].f[3], b2, b3);
             ldmatrix_x4_trans(b0, b1, b2, b3, &sm.ds[16 * ks + (mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
-            mma_bf16(dKh[0], vaf[ks][0], vaf[ks][1], vaf[ks][2], vaf[ks][3], b0, b1);
-            mma_bf16(dKh[1], vaf[ks][0], vaf[ks][1], vaf[ks][2], vaf[ks][3], b2, b3);
+            mma_bf16(dKh[0], fv[ks].f[0], fv[ks].f[1], fv[ks].f[2], fv[ks].f[3], b0, b1);
+            mma_bf16(dKh[1], fv[ks].f[0], fv[ks].f[1], fv[ks].f[2], fv[ks].f[3], b2, b3);
         }
         {
             uint32_t b0, b1, b2, b3;
