@@ -49,6 +49,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"((uint32_t)__cvta_generic_to_shared(row)));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"((uint32_t)__cvta_generic_to_shared(row)));
+}
 // D(16x8, fp32) += A(16x16, bf16, row) B(16x8, bf16, col)
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -140,13 +145,15 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
             acc[nt][0] *= l2.x; acc[nt][1] *= l2.y; acc[nt][2] *= l2.x; acc[nt][3] *= l2.y;
         }
         // += dS M'^T : B[k = j'][n = j] = M'[j][j'], read along the rows of M'
+        // (one ldmatrix.x4 fetches the two 8x8 blocks of each of two column tiles: rows j of M', 16 values of j')
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&s.m[nt * 8 + g][ks * 16 + 2 * q]);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&s.m[nt * 8 + g][ks * 16 + 8 + 2 * q]);
-                mma_bf16(acc[nt], afrag[ks][0], afrag[ks][1], afrag[ks][2], afrag[ks][3], b0, b1);
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b0, b1, b2, b3;    // (tile 2 np: b0, b2), (tile 2 np + 1: b1, b3)
+                ldmatrix_x4(b0, b1, b2, b3, &s.m[np * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)][ks * 16 + (lane >> 4) * 8]);
+                mma_bf16(acc[2 * np], afrag[ks][0], afrag[ks][1], afrag[ks][2], afrag[ks][3], b0, b2);
+                mma_bf16(acc[2 * np + 1], afrag[ks][0], afrag[ks][1], afrag[ks][2], afrag[ks][3], b1, b3);
             }
         // += dY^T R- : A[m = i][k = t] = dY[t][i] and B[k = t][n = j] = R-[t][j], both fetched transposed
         if (dy != nullptr) {
