@@ -89,14 +89,44 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const __grid_constant__ StreamMaps maps, unsigned char* __restrict__ saved,
                       int* __restrict__ range_flag, int range_ticket, int* __restrict__ residual_mark,
                       __nv_bfloat16* __restrict__ mprime, __nv_bfloat16* __restrict__ rbar, float* __restrict__ lam_out,
-                      int* __restrict__ fast_flag) {
+                      int* __restrict__ fast_flag, int pieces) {
     extern __shared__ __align__(128) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
-    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    const int bh = blockIdx.x / pieces, piece = blockIdx.x % pieces, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = warp & 3, hsel = warp >> 2;
     const int row = quad * 32 + lane;
     const int L = min((int)length[bi], Tlen);
+    // ---- sequence-parallel mode (pieces > 1, calls without a residual): a start flag cuts every dependence, so a
+    // sequence may be walked as independent pieces whose first token carries a start flag.  Cut k, k = 1..pieces-1,
+    // is the start flag nearest to k T / pieces within half a piece of it, if there is one; every CTA of the
+    // sequence finds the same cuts by itself, a CTA whose own cut does not exist has nothing to do.
+    int t_begin = 0, t_end = Tlen;
+    if (pieces > 1) {
+        const uint8_t* ns_row = new_starts + (size_t)bi * Tlen;
+        const int half = Tlen / (2 * pieces);
+        auto find_cut = [&](int k) -> int {       // position of cut k, or -1; all threads of the CTA take part
+            const int target = (int)((long long)k * Tlen / pieces);
+            const int lo = max(target - half, 1), hi = min(target + half, Tlen);
+            __syncthreads();
+            if (tid == 0) sm.nsm[0] = 0xffffffffu;
+            __syncthreads();
+            for (int t = lo + tid; t < hi; t += blockDim.x)
+                if (ns_row[t] != 0) atomicMin(&sm.nsm[0], (uint32_t)(abs(t - target) * 2 + (t > target ? 1 : 0)) << 16 | (uint32_t)(t - lo));
+            __syncthreads();
+            const uint32_t best = sm.nsm[0];
+            return best == 0xffffffffu ? -1 : lo + (int)(best & 0xffffu);
+        };
+        if (piece > 0) {
+            t_begin = find_cut(piece);
+            if (t_begin < 0) return;              // (the decision is the same for every thread)
+        }
+        for (int k = piece + 1; k < pieces; ++k) {
+            const int c = find_cut(k);
+            if (c >= 0) { t_end = c; break; }
+        }
+        __syncthreads();
+    }
     const size_t tok_stride = (size_t)H * kN;
     const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
     const size_t st_row = ((size_t)bh * kN + (row & 63)) * kN + hsel * 32;  // this thread's 32 state elements
@@ -120,7 +150,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     // ---- state into TMEM (rows 0..63 = S0 in fp32, rows 64..127 are never read) --------------
     {
         float s[32];
-        if (row < 64) {
+        if (row < 64 && t_begin == 0) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) unpack8(*reinterpret_cast<const uint4*>(s0 + st_row + c * 8), &s[c * 8]);
         } else {
@@ -148,10 +178,10 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     const int tsub = tid >> 3, jb = tid & 7;                // staging unit: tokens 32q+tsub (q=0,1), channels 8jb..8jb+7
 
     constexpr int kIssuer2 = 96;   // a thread of the warp with the least epilogue work
-    int p = 0;
+    int p = t_begin;
     bool all_saved = (saved != nullptr);   // every chunk so far was a full block with its operands saved
     uint32_t par = 0, spar = 0;   // phase parities of the product barriers and of the staging barrier
-    uint8_t flag_ahead = (tid < 64 && tid < Tlen) ? new_starts[(size_t)bi * Tlen + tid] : 0;
+    uint8_t flag_ahead = (tid < 64 && t_begin + tid < Tlen) ? new_starts[(size_t)bi * Tlen + t_begin + tid] : 0;
     // the 64 token rows from cp on of w, r, k, v, a, b into the staging tiles (thread 0; one tiled copy
     // per stream).  Rows past the chunk arrive too and are ignored.
     auto issue_stage = [&](int cp) {
@@ -161,10 +191,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             for (int m = 0; m < 6; ++m) tc::tensor_load_2d(smem + stage_off(m), &maps.m[m], h * kN, bi * Tlen + cp, &sm.bar[4]);
         }
     };
-    issue_stage(0);
+    issue_stage(t_begin);
     while (true) {
         // ================= boundary at position p: TMEM holds the state after token p-1 =================
-        const bool want_out = (p == L);
+        // (of the pieces of a sequence, the one that has walked token L - 1 holds it; L == 0: the first)
+        const bool want_out = (p == L) && (p > t_begin || t_begin == 0);
         if (quad < 2 && want_out) {
             float s[32];
             tc::tmem_ld32(lane_addr + DS + hsel * 32, s);
@@ -177,9 +208,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     *reinterpret_cast<float4*>(s_at_len + st_row + c * 4) = make_float4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
             }
         }
-        if (p >= Tlen) break;
+        if (p >= t_end) break;
         // ================= extent of this chunk =================
-        const int be = min(((p >> 6) + 1) << 6, Tlen);
+        const int be = min(((p >> 6) + 1) << 6, t_end);
         if (tid < 64) {
             // the flag byte of position p + tid was requested while the previous chunk's products ran
             const bool f = (p + tid < be) && (flag_ahead != 0);
@@ -405,7 +436,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         }
         // the rows of the next chunk start travelling: their tiles lie over buffers that are idle from
         // here to the next chunk's operand stores (the inverse and the A_ak / P_rk product are done)
-        if (p1 < Tlen) issue_stage(p1);
+        if (p1 < t_end) issue_stage(p1);
         if (quad < 2) {
             if (!tc::mbar_wait(&sm.bar[2], par)) failed = true;
             tc::fence_after_sync();
@@ -548,7 +579,18 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     StreamMaps maps;
     const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]
     if (!make_stream_maps(&maps, bases, 6, B, T, H)) return B200WKV_ELAUNCH;
-    wkv7_chunk_fwd_kernel<<<B * H, 256, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
+    // Without a residual (inference) and with fewer sequences than CTA slots, every sequence is offered to several
+    // CTAs, which cut it at start flags where there are any (see the kernel): at most 8 pieces of at least 128 tokens.
+    int pieces = 1;
+    if (residual == nullptr) {
+        const long long slots = 2LL * sm_count_of_current_device();
+        const long long seqs = (long long)B * H;
+        if (seqs < slots) pieces = (int)((2 * slots + seqs - 1) / seqs);
+        if (pieces > 8) pieces = 8;
+        if (pieces > T / 128) pieces = T / 128;
+        if (pieces < 1 || T / pieces >= 32768) pieces = 1;
+    }
+    wkv7_chunk_fwd_kernel<<<B * H * pieces, 256, SMEM_BYTES, st>>>(T, H, (const bf*)w, (const bf*)r, (const bf*)k, (const bf*)v,
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
                                                           (bf*)y, (bf*)s_out, (float*)residual,
                                                           residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
@@ -558,7 +600,7 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                                                           residual ? (bf*)((char*)residual + lay.mprime) : nullptr,
                                                           residual ? (bf*)((char*)residual + lay.rbar) : nullptr,
                                                           residual ? (float*)((char*)residual + lay.lam) : nullptr,
-                                                          residual ? (int*)((char*)residual + lay.fast) : nullptr);
+                                                          residual ? (int*)((char*)residual + lay.fast) : nullptr, pieces);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

@@ -618,3 +618,18 @@ def test_no_bounded_wait_ran_out_during_the_suite():
     """Every mbarrier wait in the tensor-core kernels is bounded and records a failure in a device
     word; after the tensor-core tests above that word must still be clear."""
     assert _lib.load().b200wkv_device_status() == 0
+
+
+def test_inference_forward_cut_at_start_flags():
+    """Few sequences, calls without a residual: the forward offers every sequence to several CTAs, which cut it at start
+    flags (a flag cuts every dependence).  Lengths on a cut, before it, behind it, zero; sequences without any flag;
+    flags only near the ends; all against the oracle."""
+    T = 1024
+    # cuts are looked for near k T / 8: flags exactly there, just beside, and far away
+    starts = [[128, 256, 384, 640, 900], [], [5, 1020], [127, 129, 511, 513, 514], [0, 300, 301, 767], [512]]
+    lengths = [T, T, 700, 513, 0, 512]
+    d = wkv7_case(6, T, 2, seed=501, s0_scale=0.5, starts=starts, lengths=lengths)
+    check_fwd_chunk(d)
+    # the benchmark's inference configuration in small: Bernoulli(1/256) flags, ragged lengths
+    d = wkv7_case(3, 2048, 2, seed=502, s0_scale=0.0, p_start=1 / 256, random_length=True)
+    check_fwd_chunk(d)
