@@ -85,7 +85,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t ld32(const bf* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 // Sums each of eight per-lane values over the warp with nine shuffles: three halving steps leave one value per lane,
 // two butterflies finish.  Returns the total of v[which] with which = 4 bit4(lane) + 2 bit3(lane) + bit2(lane).
@@ -378,7 +377,7 @@ struct Bwd6cSmem {
     uint8_t ns[2][kC6];
 };
 
-__global__ void __launch_bounds__(128, 3)
+__global__ void __launch_bounds__(128, 2)
 wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ k, const bf* __restrict__ v,
                       const bf* __restrict__ w, int w_per_token, const bf* __restrict__ u,
                       const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
@@ -461,6 +460,17 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     float du_acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     float dw_acc = 0.f;                        // constant decay: sum over tokens of the log-decay gradient (thread ch < 64)
 
+    int out_t0 = -1, out_lo = 0, out_hi = 0;     // the chunk (part) whose results wait in the result tiles
+    auto flush_results = [&]() {
+        const int t = out_t0 + srow;
+        if (out_t0 >= 0 && t < Tlen && srow >= out_lo && srow < out_hi) {
+            const size_t off = seq_base + (size_t)t * tok_stride + spiece;
+            *reinterpret_cast<uint4*>(dr + off) = *reinterpret_cast<const uint4*>(&sm.ops[0][srow][spiece]);
+            *reinterpret_cast<uint4*>(dk + off) = *reinterpret_cast<const uint4*>(&sm.ops[1][srow][spiece]);
+            *reinterpret_cast<uint4*>(dv + off) = *reinterpret_cast<const uint4*>(&sm.ops[2][srow][spiece]);
+            if (w_per_token) *reinterpret_cast<uint4*>(dw_tok + off) = *reinterpret_cast<const uint4*>(&sm.ops[3][srow][spiece]);
+        }
+    };
     auto walk = [&](auto split_tag, const int c, const int it, const int part_arg) {
         constexpr bool kSplitHere = decltype(split_tag)::value;
         const bool split_here = kSplitHere;
@@ -475,8 +485,10 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             ns_ahead = load_ns(c - 2);
             if (split_here) fetch_state(nC, stage);                   // the state behind token p_out
         } else {
-            fetch_state(c, stage);                                    // (its barrier also retires the first visit's reads)
+            __syncthreads();                                          // the first visit's suffix sums have read the tile refilled here
+            fetch_state(c, stage);
         }
+        flush_results();                                              // of the walk before this one; phase A rewrites the tiles behind S2
         const BwdStage& st = sm.st[stage];
         const int t0 = c * kC6;
         if (c == c_out && part == 0) add_ds_out();
@@ -712,17 +724,10 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
                 else if (t0 + x < Tlen && x >= lo && x < hi) dw_acc += run2;
             }
         }
-        __syncthreads();                                              // S6
-        {
-            const int t = t0 + srow;
-            if (t < Tlen && srow >= lo && srow < hi) {
-                const size_t off = seq_base + (size_t)t * tok_stride + spiece;
-                *reinterpret_cast<uint4*>(dr + off) = *reinterpret_cast<const uint4*>(&sm.ops[0][srow][spiece]);
-                *reinterpret_cast<uint4*>(dk + off) = *reinterpret_cast<const uint4*>(&sm.ops[1][srow][spiece]);
-                *reinterpret_cast<uint4*>(dv + off) = *reinterpret_cast<const uint4*>(&sm.ops[2][srow][spiece]);
-                if (w_per_token) *reinterpret_cast<uint4*>(dw_tok + off) = *reinterpret_cast<const uint4*>(&sm.ops[3][srow][spiece]);
-            }
-        }
+        // the four result tiles leave after the next barrier (the top of the next walk, or the one behind the loop)
+        out_t0 = t0;
+        out_lo = lo;
+        out_hi = hi;
     };
     for (int c = nC - 1, it = 0; c >= 0; --c, ++it) {
         if (split && c == c_out) {
@@ -732,6 +737,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             walk(std::false_type{}, c, it, 0);
         }
     }
+    __syncthreads();
+    flush_results();
     if (L == 0) add_ds_out();
 #pragma unroll
     for (int ni = 0; ni < 8; ++ni)
