@@ -134,7 +134,7 @@ int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int 
 int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int N,
                  const void* r, const void* k, const void* v, const void* w, const void* u,
                  const void* s0, const uint32_t* length, const uint8_t* new_starts,
-                 const void* dy, const void* ds_out, const void* residual, size_t residual_bytes,
+                 const void* dy, const void* ds_out, void* residual, size_t residual_bytes,
                  void* dr, void* dk, void* dv, void* dw, void* du, void* ds0, unsigned flags);
 
 /* ---------------------------------------------------------------- RWKV-4 ----

@@ -51,7 +51,7 @@ int wkv6_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* r, const vo
                    void* s_out, void* residual, int* residual_mark, int** flag, int* ticket);
 int wkv6_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
                    int per_token, const void* u, const uint32_t* length, const uint8_t* ns, const void* dy, const void* ds_out,
-                   const void* residual, const int* residual_mark, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0);
+                   void* residual, const int* residual_mark, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0);
 size_t wkv4_residual_bytes(int B, int T, int C);
 int wkv4_fwd(cudaStream_t st, int dtype, int B, int T, int C, const void* w, const void* u, const void* k, const void* v,
              const void* s0, const uint32_t* length, const uint8_t* ns, void* s_out, void* y, void* residual);
@@ -234,7 +234,7 @@ int b200wkv6_fwd(void* stream, int dtype, int version, int B, int T, int H, int 
 
 int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int N, const void* r, const void* k,
                  const void* v, const void* w, const void* u, const void* s0, const uint32_t* length,
-                 const uint8_t* new_starts, const void* dy, const void* ds_out, const void* residual,
+                 const uint8_t* new_starts, const void* dy, const void* ds_out, void* residual,
                  size_t residual_bytes, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0, unsigned flags) {
     int st = check_dims(dtype, B, T, H, N);
     if (st != B200WKV_OK) return st;
@@ -245,9 +245,9 @@ int b200wkv6_bwd(void* stream, int dtype, int version, int B, int T, int H, int 
     (void)flags;
     if (dtype == B200WKV_BF16) {
         // the forward's mark decides on the device which of the two runs; the other returns at once
-        const int* mark = residual_mark_of(const_cast<void*>(residual), b200wkv6_residual_bytes(dtype, B, T, H, N));
-        st = wkv6_chunk_bwd((cudaStream_t)stream, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy, ds_out, residual,
-                            mark, dr, dk, dv, dw, du, ds0);
+        const int* mark = residual_mark_of(residual, b200wkv6_residual_bytes(dtype, B, T, H, N));
+        st = wkv6_chunk_bwd((cudaStream_t)stream, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy, ds_out,
+                            residual, mark, dr, dk, dv, dw, du, ds0);
         if (st != B200WKV_OK) return st;
         return wkv6_seq_bwd((cudaStream_t)stream, dtype, B, T, H, r, k, v, w, version == 6, u, length, new_starts, dy, ds_out,
                             residual, dr, dk, dv, dw, du, ds0, mark);

@@ -377,17 +377,20 @@ struct Bwd6cSmem {
     uint8_t ns[2][kC6];
 };
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(128, 3)
 wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ k, const bf* __restrict__ v,
                       const bf* __restrict__ w, int w_per_token, const bf* __restrict__ u,
                       const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
                       const bf* __restrict__ dy, const bf* __restrict__ ds_out, const bf* __restrict__ ckpt,
                       const int* __restrict__ residual_mark, bf* __restrict__ dr, bf* __restrict__ dk, bf* __restrict__ dv,
-                      bf* __restrict__ dw_tok, float* __restrict__ dw_head, float* __restrict__ du_head, bf* __restrict__ ds0) {
+                      bf* __restrict__ dw_tok, float* __restrict__ dw_head, float* __restrict__ du_head, bf* __restrict__ ds0,
+                      int n_runs, int run_len, const bf* __restrict__ dsck, float* __restrict__ partial) {
     if (*residual_mark != 0) return;          // the forward fell back to the sequential kernels
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Bwd6cSmem& sm = *reinterpret_cast<Bwd6cSmem*>(smem_raw);
-    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    // n_runs > 1: a sequence is walked by n_runs CTAs, run rho = chunks [rho run_len, (rho + 1) run_len), each starting
+    // from the state gradient that the carry kernel (wkv6_carry_bwd_kernel) left for the end of its run
+    const int bh = blockIdx.x / n_runs, run = blockIdx.x % n_runs, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3, mi = lane >> 3, r8 = lane & 7;
     const int j0 = warp * 16;                 // value rows of dS^T, and key channels of the token-by-channel results
@@ -398,12 +401,24 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     const int nC = (Tlen + kC6 - 1) / kC6;
     const int c_out = L > 0 ? (L - 1) / kC6 : -1, p_out = L > 0 ? (L - 1) % kC6 : -1;
     const bool split = L > 0 && L < Tlen && p_out != kC6 - 1;      // see the forward: that chunk is walked in two parts
+    const int c_lo = run * run_len, c_hi = min(nC, c_lo + run_len);
+    if (c_lo >= c_hi) return;
 
     float acc[8][4];
+    if (run == n_runs - 1 || c_hi >= nC) {
 #pragma unroll
-    for (int ni = 0; ni < 8; ++ni)
+        for (int ni = 0; ni < 8; ++ni)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[ni][e] = 0.f;
+            for (int e = 0; e < 4; ++e) acc[ni][e] = 0.f;
+    } else {
+        const bf* src = dsck + ((size_t)bh * n_runs + run) * kN * kN;
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni) {
+            const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (size_t)(j0 + g) * kN + 8 * ni + 2 * q));
+            const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (size_t)(j0 + g + 8) * kN + 8 * ni + 2 * q));
+            acc[ni][0] = lo2.x; acc[ni][1] = lo2.y; acc[ni][2] = hi2.x; acc[ni][3] = hi2.y;
+        }
+    }
     auto add_ds_out = [&]() {
         if (ds_out == nullptr) return;
 #pragma unroll
@@ -415,7 +430,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 
     const int srow = tid >> 3, spiece = (tid & 7) * 8;
     auto issue = [&](int c, int stage) {
-        if (c >= 0) {
+        if (c >= c_lo) {
             BwdStage& st = sm.st[stage];
             const int t = c * kC6 + srow;
             const bool ok = t < Tlen;
@@ -445,9 +460,9 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         const int t = c * kC6 + tid;
         return (tid < kC6 && c >= 0 && t < Tlen) ? new_starts[(size_t)bi * Tlen + t] : (uint8_t)0;
     };
-    issue(nC - 1, 0);
-    if (tid < kC6) sm.ns[0][tid] = load_ns(nC - 1);
-    uint8_t ns_ahead = load_ns(nC - 2);
+    issue(c_hi - 1, 0);
+    if (tid < kC6) sm.ns[0][tid] = load_ns(c_hi - 1);
+    uint8_t ns_ahead = load_ns(c_hi - 2);
 
     const int ch = tid & 63, half = tid >> 6;
     const float uu_a = __bfloat162float(u[(size_t)h * kN + ch]);
@@ -729,7 +744,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         out_lo = lo;
         out_hi = hi;
     };
-    for (int c = nC - 1, it = 0; c >= 0; --c, ++it) {
+    for (int c = c_hi - 1, it = 0; c >= c_lo; --c, ++it) {
         if (split && c == c_out) {
 #pragma unroll 1
             for (int part = 1; part >= 0; --part) walk(std::true_type{}, c, it, part);   // tokens behind `length` first
@@ -739,12 +754,17 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     }
     __syncthreads();
     flush_results();
-    if (L == 0) add_ds_out();
+    if (run == 0) {
+        if (L == 0) add_ds_out();
 #pragma unroll
-    for (int ni = 0; ni < 8; ++ni)
+        for (int ni = 0; ni < 8; ++ni)
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-            ds0[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(acc[ni][e]);
+            for (int e = 0; e < 4; ++e)
+                ds0[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)] = __float2bfloat16_rn(acc[ni][e]);
+    }
+    // per-(batch, head) sums over tokens: directly, or this run's share for the reduction behind the kernel
+    float* const du_dst = n_runs == 1 ? du_head + (size_t)bh * kN : partial + ((size_t)bh * n_runs + run) * 2 * kN;
+    float* const dw_dst = n_runs == 1 ? (dw_head != nullptr ? dw_head + (size_t)bh * kN : nullptr) : du_dst + kN;
     // du: sum over this thread's token rows, then over the eight row groups of the warp
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
@@ -753,16 +773,212 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             float p = du_acc[nt][e];
 #pragma unroll
             for (int m = 4; m < 32; m <<= 1) p += __shfl_xor_sync(0xffffffffu, p, m);
-            if (g == 0) du_head[(size_t)bh * kN + j0 + 8 * nt + 2 * q + e] = p;
+            if (g == 0) du_dst[j0 + 8 * nt + 2 * q + e] = p;
         }
-    if (!w_per_token && tid < kN) dw_head[(size_t)bh * kN + tid] = dw_acc / __bfloat162float(w[(size_t)h * kN + tid]);
+    if (!w_per_token && tid < kN && dw_dst != nullptr) dw_dst[tid] = dw_acc / __bfloat162float(w[(size_t)h * kN + tid]);
+}
+
+// ------------------------------------------------------------------ the state-gradient carry
+// The only part of the backward that is sequential in T, on its own: dS0^T = dS_C^T diag(exp(c_C)) [no start in the
+// chunk] + dY^T R0 per chunk (and the cotangent of the returned state where it enters), with dS^T in accumulator
+// registers.  It leaves the state gradient at the end of every run of `run_len` chunks, from which the gradient kernel
+// above walks the runs in parallel.
+struct CarryStage6 {
+    bf r[kC6][PITCH], w[kC6][PITCH], dy[kC6][PITCH];
+};
+struct Carry6Smem {
+    CarryStage6 st[kStages6];
+    bf r0[kC6][PITCH];
+    float tot[2][kN];
+    float wc[kN];
+    unsigned startmask;
+    uint8_t ns[kStages6][kC6];
+};
+
+__global__ void __launch_bounds__(128)
+wkv6_carry_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ w, int w_per_token,
+                      const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts, const bf* __restrict__ dy,
+                      const bf* __restrict__ ds_out, const int* __restrict__ residual_mark, int n_runs, int run_len,
+                      bf* __restrict__ dsck) {
+    if (*residual_mark != 0) return;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Carry6Smem& sm = *reinterpret_cast<Carry6Smem*>(smem_raw);
+    const int bh = blockIdx.x, bi = bh / H, h = bh % H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3, mi = lane >> 3, r8 = lane & 7;
+    const int j0 = warp * 16;
+    const size_t tok_stride = (size_t)H * kN;
+    const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
+    const size_t st_base = (size_t)bh * kN * kN;
+    const int L = min((int)length[bi], Tlen);
+    const int nC = (Tlen + kC6 - 1) / kC6;
+    const int c_out = L > 0 ? (L - 1) / kC6 : -1, p_out = L > 0 ? (L - 1) % kC6 : -1;
+    const bool split = L > 0 && L < Tlen && p_out != kC6 - 1;
+    const int c_stop = run_len;        // nothing below the first run's end is needed: run 0 starts from the state left there
+
+    float acc[8][4];
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[ni][e] = 0.f;
+    const int srow = tid >> 3, spiece = (tid & 7) * 8;
+    auto issue = [&](int c) {
+        if (c >= c_stop) {
+            CarryStage6& st = sm.st[c % kStages6];
+            const int t = c * kC6 + srow;
+            const bool ok = t < Tlen;
+            const size_t off = seq_base + (size_t)(ok ? t : 0) * tok_stride + spiece;
+            cp_async16_zfill(&st.r[srow][spiece], r + off, ok);
+            if (w_per_token) cp_async16_zfill(&st.w[srow][spiece], w + off, ok);
+            cp_async16_zfill(&st.dy[srow][spiece], dy != nullptr ? dy + off : r + off, ok && dy != nullptr);
+        }
+        cp_async_commit();
+    };
+    auto load_ns = [&](int c) -> uint8_t {
+        const int t = c * kC6 + tid;
+        return (tid < kC6 && c >= 0 && t < Tlen) ? new_starts[(size_t)bi * Tlen + t] : (uint8_t)0;
+    };
+    issue(nC - 1);
+    issue(nC - 2);
+    if (tid < kC6) {
+        sm.ns[(nC - 1) % kStages6][tid] = load_ns(nC - 1);
+        if (nC >= 2) sm.ns[(nC - 2) % kStages6][tid] = load_ns(nC - 2);
+    }
+    uint8_t ns_ahead = load_ns(nC - 3);
+    const int ch = tid & 63, half = tid >> 6;
+    const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
+
+    auto walk = [&](auto split_tag, const int c, const int part_arg) {
+        constexpr bool kSplitHere = decltype(split_tag)::value;
+        const int part = kSplitHere ? part_arg : 0;
+        const int lo = (kSplitHere && part == 1) ? p_out + 1 : 0, hi = (kSplitHere && part == 0) ? p_out + 1 : kC6;
+        const CarryStage6& st = sm.st[c % kStages6];
+        const int t0 = c * kC6;
+        if (!kSplitHere || part == 1) {
+            cp_async_wait<1>();
+            __syncthreads();
+            issue(c - 2);
+            if (tid < kC6 && c - 2 >= 0) sm.ns[(c - 2) % kStages6][tid] = ns_ahead;
+            ns_ahead = load_ns(c - 3);
+        } else {
+            __syncthreads();
+        }
+        if (c == c_out && part == 0 && ds_out != nullptr) {
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    acc[ni][e] += __bfloat162float(ds_out[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)]);
+        }
+        if (warp == 0) {
+            const unsigned m = __ballot_sync(0xffffffffu, lane < kC6 && sm.ns[c % kStages6][lane] != 0);
+            if (lane == 0) sm.startmask = m;
+        }
+        float lw[8], cl[8];
+        float run = 0.f;
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const int t = 8 * half + tt;
+            const bool ok = t0 + t < Tlen && t >= lo && t < hi;
+            lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
+            run += lw[tt];
+            cl[tt] = run;
+        }
+        sm.tot[half][ch] = run;
+        __syncthreads();
+        {
+            const unsigned starts = sm.startmask;
+            auto seg_of = [&](int t) { return __popc(starts & ((2u << t) - 1u)); };
+            const int seg_last = seg_of(hi - 1), seg_base = lo > 0 ? seg_of(lo - 1) : 0;
+            const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
+            const float base = half ? c_m : 0.f;
+            if (half) sm.wc[ch] = seg_last == seg_base ? __expf(c_C) : 0.f;
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+                const int t = 8 * half + tt;
+                const bool in_part = t >= lo && t < hi;
+                const float c_prev = base + cl[tt] - lw[tt];
+                const float rv = in_part ? __bfloat162float(st.r[t][ch]) : 0.f;
+                sm.r0[t][ch] = __float2bfloat16_rn(seg_of(t) == seg_base ? rv * __expf(c_prev) : 0.f);
+            }
+        }
+        __syncthreads();
+        {
+            uint32_t ya[4];
+            ldmatrix_x4_trans(ya[0], ya[1], ya[2], ya[3], &st.dy[(mi >> 1) * 8 + r8][j0 + (mi & 1) * 8]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                const float2 w0 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 2 * q]);
+                const float2 w1 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 8 + 2 * q]);
+                acc[2 * np][0] *= w0.x; acc[2 * np][1] *= w0.y; acc[2 * np][2] *= w0.x; acc[2 * np][3] *= w0.y;
+                acc[2 * np + 1][0] *= w1.x; acc[2 * np + 1][1] *= w1.y; acc[2 * np + 1][2] *= w1.x; acc[2 * np + 1][3] *= w1.y;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, &sm.r0[(mi & 1) * 8 + r8][(2 * np + (mi >> 1)) * 8]);
+                mma_bf16(acc[2 * np], ya[0], ya[1], ya[2], ya[3], b0, b1);
+                mma_bf16(acc[2 * np + 1], ya[0], ya[1], ya[2], ya[3], b2, b3);
+            }
+        }
+    };
+    for (int c = nC - 1; c >= c_stop - 1; --c) {
+        // the state gradient behind the last chunk of a run (before anything of that chunk is applied), for the CTA of
+        // the gradient kernel that walks the run
+        if ((c + 1) % run_len == 0 && c + 1 < nC) {
+            bf* dst = dsck + ((size_t)bh * n_runs + c / run_len) * kN * kN;
+#pragma unroll
+            for (int ni = 0; ni < 8; ++ni) {
+                *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g) * kN + 8 * ni + 2 * q) = pack2(acc[ni][0], acc[ni][1]);
+                *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g + 8) * kN + 8 * ni + 2 * q) = pack2(acc[ni][2], acc[ni][3]);
+            }
+        }
+        if (c < c_stop) break;
+        if (split && c == c_out) {
+#pragma unroll 1
+            for (int part = 1; part >= 0; --part) walk(std::true_type{}, c, part);
+        } else {
+            walk(std::false_type{}, c, 0);
+        }
+    }
+    cp_async_wait<0>();
+}
+
+// du (and the gradient of a constant decay) of a (batch, head): the runs' shares added in a fixed order
+__global__ void wkv6_reduce_runs_kernel(int BH, int n_runs, const float* __restrict__ partial, const int* __restrict__ residual_mark,
+                                        float* __restrict__ du_head, float* __restrict__ dw_head) {
+    if (*residual_mark != 0) return;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= BH * kN) return;
+    const int bh = idx / kN, i = idx % kN;
+    float su = 0.f, sw = 0.f;
+    for (int rho = 0; rho < n_runs; ++rho) {
+        su += partial[((size_t)bh * n_runs + rho) * 2 * kN + i];
+        if (dw_head != nullptr) sw += partial[((size_t)bh * n_runs + rho) * 2 * kN + kN + i];
+    }
+    du_head[idx] = su;
+    if (dw_head != nullptr) dw_head[idx] = sw;
 }
 
 }  // namespace
 
-size_t wkv6_chunk_residual_bytes(int B, int T, int H) {
-    return (size_t)B * H * ((T + kC6 - 1) / kC6 + 1) * kN * kN * sizeof(bf);   // every chunk, and the second part of a split one
+// How the backward cuts a sequence: runs of 16 chunks (256 tokens) once there are at least two of them.
+constexpr int kRunLen = 16;
+static int runs_of(int T) {
+    const int nC = (T + kC6 - 1) / kC6;
+    return nC >= 2 * kRunLen ? (nC + kRunLen - 1) / kRunLen : 1;
 }
+struct Layout6 {
+    size_t states, dsck, partial, end;
+};
+static Layout6 layout6(int B, int T, int H) {
+    const size_t nC = (size_t)(T + kC6 - 1) / kC6, runs = (size_t)runs_of(T), tile = (size_t)kN * kN * sizeof(bf);
+    Layout6 l;
+    l.states = 0;                                              // every chunk's entering state, and the second part of a split one
+    l.dsck = l.states + (size_t)B * H * (nC + 1) * tile;       // the state gradient at the end of every run (written by the backward)
+    l.partial = l.dsck + (size_t)B * H * runs * tile;          // the runs' shares of du and of a constant decay's gradient (fp32)
+    l.end = l.partial + (size_t)B * H * runs * 2 * kN * sizeof(float);
+    return l;
+}
+
+size_t wkv6_chunk_residual_bytes(int B, int T, int H) { return layout6(B, T, H).end; }
 
 int wkv6_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
                    int per_token, const void* u, const void* s0, const uint32_t* length, const uint8_t* ns, void* y,
@@ -780,16 +996,36 @@ int wkv6_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* r, const vo
 
 int wkv6_chunk_bwd(cudaStream_t st, int B, int T, int H, const void* r, const void* k, const void* v, const void* w,
                    int per_token, const void* u, const uint32_t* length, const uint8_t* ns, const void* dy, const void* ds_out,
-                   const void* residual, const int* residual_mark, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0) {
+                   void* residual, const int* residual_mark, void* dr, void* dk, void* dv, void* dw, void* du, void* ds0) {
     static DeviceOnce smem_attr;
-    if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv6_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd6cSmem)); }))
+    if (!smem_attr.ok([]() {
+            cudaError_t e = cudaFuncSetAttribute(wkv6_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd6cSmem));
+            if (e != cudaSuccess) return e;
+            return cudaFuncSetAttribute(wkv6_carry_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Carry6Smem));
+        }))
         return B200WKV_ELAUNCH;
-    wkv6_chunk_bwd_kernel<<<B * H, 128, sizeof(Bwd6cSmem), st>>>(T, H, (const bf*)r, (const bf*)k, (const bf*)v, (const bf*)w, per_token,
-                                                                (const bf*)u, length, ns, (const bf*)dy, (const bf*)ds_out,
-                                                                (const bf*)residual, residual_mark, (bf*)dr, (bf*)dk, (bf*)dv,
-                                                                per_token ? (bf*)dw : nullptr, per_token ? nullptr : (float*)dw,
-                                                                (float*)du, (bf*)ds0);
-    return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
+    const Layout6 lay = layout6(B, T, H);
+    char* base = static_cast<char*>(residual);
+    const int n_runs = runs_of(T);
+    bf* dsck = reinterpret_cast<bf*>(base + lay.dsck);
+    float* partial = reinterpret_cast<float*>(base + lay.partial);
+    float* dw_head = per_token ? nullptr : (float*)dw;
+    if (n_runs > 1) {
+        wkv6_carry_bwd_kernel<<<B * H, 128, sizeof(Carry6Smem), st>>>(T, H, (const bf*)r, (const bf*)w, per_token, length, ns, (const bf*)dy,
+                                                                     (const bf*)ds_out, residual_mark, n_runs, kRunLen, dsck);
+        if (cudaGetLastError() != cudaSuccess) return B200WKV_ELAUNCH;
+    }
+    wkv6_chunk_bwd_kernel<<<B * H * n_runs, 128, sizeof(Bwd6cSmem), st>>>(
+        T, H, (const bf*)r, (const bf*)k, (const bf*)v, (const bf*)w, per_token, (const bf*)u, length, ns, (const bf*)dy,
+        (const bf*)ds_out, (const bf*)(base + lay.states), residual_mark, (bf*)dr, (bf*)dk, (bf*)dv, per_token ? (bf*)dw : nullptr,
+        dw_head, (float*)du, (bf*)ds0, n_runs, n_runs > 1 ? kRunLen : (T + kC6 - 1) / kC6, dsck, partial);
+    if (cudaGetLastError() != cudaSuccess) return B200WKV_ELAUNCH;
+    if (n_runs > 1) {
+        const int total = B * H * kN;
+        wkv6_reduce_runs_kernel<<<(total + 255) / 256, 256, 0, st>>>(B * H, n_runs, partial, residual_mark, (float*)du, dw_head);
+        if (cudaGetLastError() != cudaSuccess) return B200WKV_ELAUNCH;
+    }
+    return B200WKV_OK;
 }
 
 }  // namespace b200wkv

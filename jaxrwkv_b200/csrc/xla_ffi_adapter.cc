@@ -151,17 +151,22 @@ ffi::Error Wkv6Fwd(cudaStream_t stream, Buf r, Buf k, Buf v, Buf w, Buf u, Buf s
                      out->untyped_data(), new_s->untyped_data(), residual->untyped_data(), residual->size_bytes(), 0u),
         "wkv6-fwd");
 }
-// "wkv6-bwd-*": (r, k, v, w, u, s, length, new_starts, gy, residual, gs_out) -> (gr, gk, gv, gw, gu, gs)
+// "wkv6-bwd-*": (r, k, v, w, u, s, length, new_starts, gy, residual, gs_out) -> (gr, gk, gv, gw, gu, gs, residual)
+// The backward writes into the residual (state gradients at the ends of the runs it walks in parallel), so operand 9
+// is donated to a seventh result: input_output_aliases={9: 6}.
 template <int CODE>
 ffi::Error Wkv6Bwd(cudaStream_t stream, Buf r, Buf k, Buf v, Buf w, Buf u, Buf s, Buf length, Buf new_starts, Buf gy,
-                   Buf residual, Buf gs_out, Res gr, Res gk, Res gv, Res gw, Res gu, Res gs, uint64_t B, uint64_t T, uint64_t H,
-                   uint64_t version) {
+                   Buf residual, Buf gs_out, Res gr, Res gk, Res gv, Res gw, Res gu, Res gs, Res residual_out, uint64_t B,
+                   uint64_t T, uint64_t H, uint64_t version) {
     if (!all_dtype<CODE>(r, k, v, w, u, s, gy, gs_out)) return ffi::Error::InvalidArgument("wkv6-bwd: operand element type does not match the target");
+    if (residual_out->untyped_data() != residual.untyped_data())
+        return ffi::Error::InvalidArgument("wkv6-bwd: the residual operand must be aliased to the last result (input_output_aliases={9: 6})");
     return status_to_error(
         b200wkv6_bwd(stream, CODE, (int)version, (int)B, (int)T, (int)H, head_size(k), r.untyped_data(), k.untyped_data(),
                      v.untyped_data(), w.untyped_data(), u.untyped_data(), s.untyped_data(), as_u32(length), as_u8(new_starts),
-                     gy.untyped_data(), gs_out.untyped_data(), residual.untyped_data(), residual.size_bytes(), gr->untyped_data(),
-                     gk->untyped_data(), gv->untyped_data(), gw->untyped_data(), gu->untyped_data(), gs->untyped_data(), 0u),
+                     gy.untyped_data(), gs_out.untyped_data(), residual_out->untyped_data(), residual_out->size_bytes(),
+                     gr->untyped_data(), gk->untyped_data(), gv->untyped_data(), gw->untyped_data(), gu->untyped_data(),
+                     gs->untyped_data(), 0u),
         "wkv6-bwd");
 }
 
@@ -229,8 +234,8 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV7StepF32, Wkv7Step<B200WKV_F32>, (bind_buffers<
 XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV7StepBF16, Wkv7Step<B200WKV_BF16>, (bind_buffers<9, 2>() B200WKV_STEP));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV6FwdF32, Wkv6Fwd<B200WKV_F32>, (bind_buffers<8, 3>() B200WKV_BTHV));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV6FwdBF16, Wkv6Fwd<B200WKV_BF16>, (bind_buffers<8, 3>() B200WKV_BTHV));
-XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV6BwdF32, Wkv6Bwd<B200WKV_F32>, (bind_buffers<11, 6>() B200WKV_BTHV));
-XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV6BwdBF16, Wkv6Bwd<B200WKV_BF16>, (bind_buffers<11, 6>() B200WKV_BTHV));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV6BwdF32, Wkv6Bwd<B200WKV_F32>, (bind_buffers<11, 7>() B200WKV_BTHV));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(WKV6BwdBF16, Wkv6Bwd<B200WKV_BF16>, (bind_buffers<11, 7>() B200WKV_BTHV));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TokenShiftFwdF32, ShiftFwd<B200WKV_F32>, (bind_buffers<5, 2>() B200WKV_BTDM));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TokenShiftFwdBF16, ShiftFwd<B200WKV_BF16>, (bind_buffers<5, 2>() B200WKV_BTDM));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TokenShiftBwdF32, ShiftBwd<B200WKV_F32>, (bind_buffers<7, 3>() B200WKV_BTDM));

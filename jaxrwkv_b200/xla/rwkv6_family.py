@@ -44,8 +44,10 @@ def make_operator(version):
         like = lambda x: jax.ShapeDtypeStruct(x.shape, x.dtype)
         part = jax.ShapeDtypeStruct((B, H, N), jnp.float32)      # per-batch partial sums of the shared operands' gradients
         fw = w.reshape(k.shape) if per_token else _hn(w, H, N, dtype)
-        gr, gk, gv, gw, gu, gs = jax.ffi.ffi_call(
-            f"wkv6-bwd-{dtype_str(dtype)}", (like(r), like(k), like(v), like(k) if per_token else part, part, like(s)),
+        # the kernel uses part of the residual as scratch: operand 9 is donated to a seventh result
+        gr, gk, gv, gw, gu, gs, _ = jax.ffi.ffi_call(
+            f"wkv6-bwd-{dtype_str(dtype)}", (like(r), like(k), like(v), like(k) if per_token else part, part, like(s), like(residual)),
+            input_output_aliases={9: 6},
         )(r, k, v, fw, _hn(u, H, N, dtype), s, length, new_starts, gy.astype(dtype), residual, gs_out.astype(dtype), **attrs(B, T, H))
         fold = lambda g, ref: (g.sum(0).reshape(H, N, 1).sum(1, keepdims=True) if ref.shape[1] == 1 else g.sum(0).reshape(H, N, 1)).astype(ref.dtype)
         gw = gw.reshape(w.shape) if per_token else fold(gw, w)
