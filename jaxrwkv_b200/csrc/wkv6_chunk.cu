@@ -15,7 +15,8 @@
 // tokens because the per-channel decay is unbounded: referenced to the chunk's middle the scaling factors stay
 // below exp(8 |lw|), which fp32 / bf16 hold for |lw| <= 10 per token (decay >= 4.5e-5); a chunk beyond that, or a
 // decay above 1, makes the kernel leave its ticket in a flag and the token-sequential kernels (wkv6_seq.cu) redo the
-// call.  A `length` inside a chunk splits that chunk in two parts that are walked like two chunks.  tcgen05 does not apply: its smallest tile is 64 tokens.
+// call.  A `length` inside a chunk splits that chunk in two parts that are walked like two chunks.  tcgen05 does not
+// apply: its smallest tile is 64 tokens.
 //
 // Semantics: BaseRWKV.inner_loop of jaxrwkv, src/jaxrwkv/rwkv6.py:174-191, rwkv5_2.py:164-180, rwkv5.py:161-177.
 #include <type_traits>
