@@ -202,3 +202,47 @@ def test_time_mixing_layer_gradients_match_cpu_autograd(golden):
         assert (a is None) == (b is None), i
         if a is not None:
             assert rel_err(a.cpu().numpy(), b.numpy()) < 2e-4, i
+
+
+def test_mix_kernels_at_benchmark_size_on_row_slices():
+    """8 x 4096 tokens, 32 heads, bf16 (every thread walks ~28 rows): forward results and stream gradients on a
+    random subset of rows against the plain-torch rendition; parameter gradients, which sum over all rows, against
+    the same sums accumulated in fp64 over row blocks."""
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(21)
+    B, T, H = 8, 4096, 32
+    C = H * 64
+    rn = lambda *s: torch.randn(*s, generator=gen, device=dev).to(torch.bfloat16)
+    k, wl, al, v, vf, vl, y, r, g = (rn(B, T, C).requires_grad_(True) for _ in range(9))
+    w0, a0, v0, k_k, k_a, ln_w, ln_b = (rn(C).requires_grad_(True) for _ in range(7))
+    r_k = (0.3 * rn(H, 64)).detach().requires_grad_(True)
+    cot = [rn(B, T, C) for _ in range(6)]
+    pre = tm.mix_pre(k, wl, al, v, vf, vl, w0, a0, v0, k_k, k_a, H)
+    post = tm.mix_post(y, r, pre[1], pre[2], g, ln_w, ln_b, r_k, H)
+    leaves = [k, wl, al, v, vf, vl, y, r, g, w0, a0, v0, k_k, k_a, ln_w, ln_b, r_k]
+    grads = torch.autograd.grad(list(pre) + [post], leaves, cot)
+    rows = torch.randperm(B * T, generator=torch.Generator().manual_seed(3))[:257].to(dev)
+    flat = lambda t: t.reshape(B * T, C)
+    # streams: the subset of rows only (every op is row-wise)
+    sub = [flat(t.detach())[rows].double().cpu().requires_grad_(True) for t in leaves[:9]]
+    par = [t.detach().double().cpu().requires_grad_(True) for t in leaves[9:]]
+    pre_r = ref_pre(sub[0], sub[1], sub[2], sub[3], sub[4], sub[5], par[0], par[1], par[2], par[3], par[4], H)
+    post_r = ref_post(sub[6], sub[7], pre_r[1], pre_r[2], sub[8], par[5], par[6], par[7], H)
+    cot_r = [flat(c)[rows].double().cpu() for c in cot]
+    grads_r = torch.autograd.grad(list(pre_r) + [post_r], sub, cot_r)
+    for i, (got, want) in enumerate(zip(list(pre) + [post], list(pre_r) + [post_r])):
+        assert rel_err(flat(got.detach())[rows].float().cpu().numpy(), want.detach().numpy()) < 1.5e-2, ("out", i)
+    for i, (got, want) in enumerate(zip(grads[:9], grads_r)):
+        assert rel_err(flat(got)[rows].float().cpu().numpy(), want.numpy()) < 3e-2, ("stream grad", i)
+    # parameters: fp64 sums over all rows, in blocks
+    acc = [torch.zeros(p.shape, dtype=torch.float64) for p in par]
+    for lo in range(0, B * T, 4096):
+        blk = [flat(t.detach())[lo:lo + 4096].double() for t in leaves[:9]]
+        pb = [t.detach().double().requires_grad_(True) for t in leaves[9:]]
+        pr = ref_pre(blk[0], blk[1], blk[2], blk[3], blk[4], blk[5], pb[0], pb[1], pb[2], pb[3], pb[4], H)
+        po = ref_post(blk[6], blk[7], pr[1], pr[2], blk[8], pb[5], pb[6], pb[7], H)
+        gb = torch.autograd.grad(list(pr) + [po], pb, [flat(c)[lo:lo + 4096].double() for c in cot])
+        for a_, g_ in zip(acc, gb):
+            a_ += g_.cpu()
+    for i, (got, want) in enumerate(zip(grads[9:], acc)):
+        assert rel_err(got.float().cpu().numpy(), want.numpy()) < 3e-2, ("param grad", i)
