@@ -42,6 +42,7 @@ inline size_t chunk_saved_offset_floats(int B, int T, int H) {
 }
 // What the carry / gradient split of the backward adds behind the saved tiles (see wkv7_carry.cu, wkv7_grad.cu):
 //   [B*H][ceil(T/64)][64][64] bf16  M' = W~^T B^ of every saved block: S_C = S0 diag(L_C) + S0 M' + (terms without S0)
+//                                   (8 column blocks of [64 rows][16 bytes], like the saved tiles)
 //   [B*T][H*64]               bf16  R- = R~ + P_rb W~ (token rows, laid out like the streams): y_t = R-_t S0^T + ...
 //   [B*H][ceil(T/64)][64]     fp32  L_C, the decay over the whole block
 //   [B*H][ceil(T/64)][64][64] bf16  scratch of the backward: the state gradient leaving every block

@@ -109,6 +109,14 @@ __device__ __forceinline__ void tensor_load_2d(void* dst_smem, const void* tmap,
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// Tiled copy of one box from shared memory to a 2-D tensor map (same rules for x); completion is tracked per
+// thread in bulk groups.
+__device__ __forceinline__ void tensor_store_2d(const void* tmap, int x, int y, const void* src_smem) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y), "r"(smem_u32(src_smem))
+                 : "memory");
+}
 // shared -> global; completion is tracked per thread in bulk groups
 __device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(__cvta_generic_to_global(dst_gmem)),

@@ -87,7 +87,7 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
             const size_t slot = (size_t)bh * nBlk + blk;
             for (int c = tid; c < 512; c += 128) {
                 const int rr = c >> 3, c8 = (c & 7) * 8;
-                cp_async16(&s.m[rr][c8], mprime + (slot * kN + rr) * kN + c8);
+                cp_async16(&s.m[rr][c8], mprime + slot * (kN * kN) + (size_t)(c & 7) * (kC * 8) + rr * 8);   // 8 column blocks of [64 rows][8]
                 cp_async16(&s.rb[rr][c8], rbar + seq_base + (size_t)(blk * kC + rr) * tok_stride + c8);
                 if (dy != nullptr) cp_async16(&s.dy[rr][c8], dy + seq_base + (size_t)(blk * kC + rr) * tok_stride + c8);
             }

@@ -51,6 +51,13 @@ constexpr int OFF_LF = OFF_AR;                           // fp32 A_ab
 constexpr int OFF_X = OFF_LF + LF_PITCH * 64 * 4;        // fp32 (I - A_ab)^-1
 constexpr int OFF_SCR = OFF_X + LF_PITCH * 64 * 4;       // scratch of the inverse
 constexpr int OFF_CUM = OFF_TP;
+// Result tiles of a chunk, written by the last epilogue over slabs whose products are done and that no copy to the
+// residual reads (V, and G = W~), and sent to global memory by bulk copies: the 64 output rows as [64][128 bytes]
+// with the 128-byte swizzle of the tiled copy (piece index XOR row mod 8), and M' as 8 column blocks of [64 rows]
+// [16 bytes], the layout of the saved tiles.
+constexpr int OFF_YT = (OFF_V + 1023) / 1024 * 1024;
+constexpr int OFF_MT = OFF_YT + kC * kN * 2;
+static_assert(OFF_MT + GTILE <= OFF_M2A + SLAB64, "result tiles must lie over V and G");
 // Staging tiles for the raw rows of the NEXT chunk (6 streams x 64 tokens x 128 bytes), filled by tiled
 // bulk copies once the inverse is done: tiles 0..4 over AR + BK + S0, tile 5 over the P_rk half of M2A.
 constexpr int STG_TILE = kC * kN * 2;
@@ -86,11 +93,12 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
                       __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
-                      const __grid_constant__ StreamMaps maps, unsigned char* __restrict__ saved,
+                      const __grid_constant__ StreamMaps maps, const __grid_constant__ CUtensorMap y_map,
+                      unsigned char* __restrict__ saved,
                       int* __restrict__ range_flag, int range_ticket, int* __restrict__ residual_mark,
                       __nv_bfloat16* __restrict__ mprime, __nv_bfloat16* __restrict__ rbar, float* __restrict__ lam_out,
                       int* __restrict__ fast_flag, int pieces) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];   // (the swizzle of the output tile is a function of the address)
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
     const int bh = blockIdx.x / pieces, piece = blockIdx.x % pieces, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -181,6 +189,18 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     int p = t_begin;
     bool all_saved = (saved != nullptr);   // every chunk so far was a full block with its operands saved
     uint32_t par = 0, spar = 0;   // phase parities of the product barriers and of the staging barrier
+    // result tiles of the chunk just finished, waiting in shared memory for the next CTA barrier
+    bool pend_y = false, pend_m = false;
+    int pend_p = 0;
+    size_t pend_slot = 0;
+    auto send_tiles = [&]() {   // behind a CTA barrier that follows the epilogue's stores
+        if (warp == 7 && lane == 0 && (pend_y || pend_m)) {
+            if (pend_y) tc::tensor_store_2d(&y_map, h * kN, bi * Tlen + pend_p, smem + OFF_YT);
+            if (pend_m) tc::bulk_store(mprime + pend_slot * (kN * kN), smem + OFF_MT, GTILE);
+            tc::bulk_commit();
+        }
+        pend_y = pend_m = false;
+    };
     uint8_t flag_ahead = (tid < 64 && t_begin + tid < Tlen) ? new_starts[(size_t)bi * Tlen + t_begin + tid] : 0;
     // the 64 token rows from cp on of w, r, k, v, a, b into the staging tiles (thread 0; one tiled copy
     // per stream).  Rows past the chunk arrive too and are ignored.
@@ -218,6 +238,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             if (lane == 0) sm.nsm[warp] = m;
         }
         __syncthreads();   // nsm visible; previous chunk's shared-memory readers are done
+        send_tiles();
         const uint64_t mask = (uint64_t)sm.nsm[0] | ((uint64_t)sm.nsm[1] << 32);
         const bool reset_here = (mask & 1ull) != 0;
         int p1 = be;
@@ -288,6 +309,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             sm.tot[tid] = t2;
             sm.lam[tid] = ex2(t2);
         }
+        if (warp == 7) tc::bulk_wait_read<0>();   // the result tiles have left the slabs that are written next
         __syncthreads();
         // ================= scaled operands into the slabs =================
         {
@@ -490,20 +512,27 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             float yv[32];
             tc::tmem_ld32(lane_addr + D2 + hsel * 32, yv);
             tc::tmem_wait_ld();
-            if (t < n) {
+            if (n == kC) {        // a full block leaves as one tiled copy out of shared memory
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(smem + OFF_YT + t * 128 + (((hsel * 4 + c) ^ (t & 7)) << 4)) = pack8(&yv[c * 8]);
+            } else if (t < n) {
                 __nv_bfloat16* dst = y + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&yv[c * 8]);
             }
         }
+        pend_y = (n == kC);
+        pend_p = p;
+        pend_m = (keep != nullptr);
+        pend_slot = blk_slot;
         if (keep != nullptr) {
             float m[32];
             if (quad < 2) {       // M'[j][j'], row j = this thread's lane
                 tc::tmem_ld32(lane_addr + D1 + hsel * 32, m);
                 tc::tmem_wait_ld();
-                __nv_bfloat16* dst = mprime + (blk_slot * kN + row) * kN + hsel * 32;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&m[c * 8]);
+                for (int c = 0; c < 4; ++c) slab_store(smem + OFF_MT, GCB, row, hsel * 4 + c, pack8(&m[c * 8]));
             } else {              // R-_t = R~_t + (P_rb W~)_t on top of the R~ row stored at the start of the chunk
                 const int t = row - 64;
                 tc::tmem_ld32(lane_addr + D1 + 64 + hsel * 32, m);
@@ -519,11 +548,14 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 }
             }
         }
+        tc::fence_async_smem();   // the result tiles are read by bulk copies
         tc::fence_before_sync();
         if (warp == 7) tc::bulk_wait_read<0>();   // the slabs copied out may be rewritten after the next barrier
         p = p1;
         par ^= 1u;
     }
+    __syncthreads();
+    send_tiles();   // of the last chunk
     if (fast_flag != nullptr && tid == 0) fast_flag[bh] = all_saved ? 1 : 0;
     if (warp == 7) tc::bulk_wait_all<0>();   // every copy to the residual has landed before the CTA retires
     if (failed) atomicExch(&g_status, 1);
@@ -579,6 +611,9 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     StreamMaps maps;
     const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]
     if (!make_stream_maps(&maps, bases, 6, B, T, H)) return B200WKV_ELAUNCH;
+    StreamMaps out_maps;                         // m[0]: the outputs, with the 128-byte swizzle of the kernel's output tile
+    const void* out_bases[1] = {y};
+    if (!make_stream_maps(&out_maps, out_bases, 1, B, T, H, /*swizzle128=*/true)) return B200WKV_ELAUNCH;
     // Without a residual (inference) and with fewer sequences than CTA slots, every sequence is offered to several
     // CTAs, which cut it at start flags where there are any (see the kernel): at most 8 pieces of at least 128 tokens.
     int pieces = 1;
@@ -594,7 +629,7 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
                                                           (bf*)y, (bf*)s_out, (float*)residual,
                                                           residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
-                                                          maps,
+                                                          maps, out_maps.m[0],
                                                           residual ? (unsigned char*)((float*)residual + chunk_saved_offset_floats(B, T, H)) : nullptr,
                                                           *range_flag, *range_ticket, residual_mark,
                                                           residual ? (bf*)((char*)residual + lay.mprime) : nullptr,
