@@ -117,6 +117,15 @@ __device__ __forceinline__ void tensor_store_2d(const void* tmap, int x, int y, 
                  "r"(x), "r"(y), "r"(smem_u32(src_smem))
                  : "memory");
 }
+// The same with an element-wise add onto what global memory holds (the element type is the tensor map's).
+__device__ __forceinline__ void tensor_reduce_add_2d(const void* tmap, int x, int y, const void* src_smem) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y), "r"(smem_u32(src_smem))
+                 : "memory");
+}
+// Orders this thread's earlier generic-proxy writes to global memory before later async-proxy (bulk copy) accesses.
+__device__ __forceinline__ void fence_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 // shared -> global; completion is tracked per thread in bulk groups
 __device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(__cvta_generic_to_global(dst_gmem)),

@@ -57,6 +57,8 @@ constexpr int OFF_CUM = OFF_TP;
 // [16 bytes], the layout of the saved tiles.
 constexpr int OFF_YT = (OFF_V + 1023) / 1024 * 1024;
 constexpr int OFF_MT = OFF_YT + kC * kN * 2;
+constexpr int OFF_RT = (OFF_BH + 1023) / 1024 * 1024;   // P_rb W~ (token rows, swizzled like the outputs) over B^, K^
+static_assert(OFF_RT + kC * kN * 2 <= OFF_SA, "the P_rb W~ tile must lie over B^ and K^");
 static_assert(OFF_MT + GTILE <= OFF_M2A + SLAB64, "result tiles must lie over V and G");
 // Staging tiles for the raw rows of the NEXT chunk (6 streams x 64 tokens x 128 bytes), filled by tiled
 // bulk copies once the inverse is done: tiles 0..4 over AR + BK + S0, tile 5 over the P_rk half of M2A.
@@ -93,7 +95,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       const __nv_bfloat16* __restrict__ s0, const uint32_t* __restrict__ length,
                       const uint8_t* __restrict__ new_starts, __nv_bfloat16* __restrict__ y,
                       __nv_bfloat16* __restrict__ s_out, float* __restrict__ ckpt, float* __restrict__ s_at_len,
-                      const __grid_constant__ StreamMaps maps, const __grid_constant__ CUtensorMap y_map,
+                      const __grid_constant__ StreamMaps maps, const __grid_constant__ CUtensorMap y_map, const __grid_constant__ CUtensorMap rbar_map,
                       unsigned char* __restrict__ saved,
                       int* __restrict__ range_flag, int range_ticket, int* __restrict__ residual_mark,
                       __nv_bfloat16* __restrict__ mprime, __nv_bfloat16* __restrict__ rbar, float* __restrict__ lam_out,
@@ -196,7 +198,11 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
     auto send_tiles = [&]() {   // behind a CTA barrier that follows the epilogue's stores
         if (warp == 7 && lane == 0 && (pend_y || pend_m)) {
             if (pend_y) tc::tensor_store_2d(&y_map, h * kN, bi * Tlen + pend_p, smem + OFF_YT);
-            if (pend_m) tc::bulk_store(mprime + pend_slot * (kN * kN), smem + OFF_MT, GTILE);
+            if (pend_m) {
+                tc::bulk_store(mprime + pend_slot * (kN * kN), smem + OFF_MT, GTILE);
+                // R- = R~ + P_rb W~: added in bf16 onto the R~ rows that went to global memory when the operands were scaled
+                tc::tensor_reduce_add_2d(&rbar_map, h * kN, bi * Tlen + pend_p, smem + OFF_RT);
+            }
             tc::bulk_commit();
         }
         pend_y = pend_m = false;
@@ -340,6 +346,7 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                     // to the R- rows in global memory, where P_rb W~ is added at the end of the chunk
                     slab_store(smem + OFF_SA, CB64, t, jb, a_t);
                     *reinterpret_cast<uint4*>(rbar + seq_base + (size_t)(p + t) * tok_stride + jb * 8) = r_t;
+                    tc::fence_async_global();   // a bulk copy adds onto these rows at the end of the chunk
                 }
                 slab_store(smem + OFF_BK, CB128, t, jb, scale8(raw[q][4], eI));
                 slab_store(smem + OFF_BK, CB128, 64 + t, jb, scale8(raw[q][1], eI));
@@ -499,12 +506,6 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
             tc::commit(&sm.bar[3]);
         }
         if (tid < 64) flag_ahead = (p1 + tid < Tlen) ? new_starts[(size_t)bi * Tlen + p1 + tid] : 0;   // next chunk's start flags
-        uint4 r_old[4];   // the R~ row stored at the start of the chunk, asked for while the products run
-        if (keep != nullptr && quad >= 2) {
-            const __nv_bfloat16* src = rbar + seq_base + (size_t)(p + row - 64) * tok_stride + hsel * 32;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) r_old[c] = *reinterpret_cast<const uint4*>(src + c * 8);
-        }
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
         if (quad >= 2) {
@@ -537,15 +538,9 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 const int t = row - 64;
                 tc::tmem_ld32(lane_addr + D1 + 64 + hsel * 32, m);
                 tc::tmem_wait_ld();
-                __nv_bfloat16* dst = rbar + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float old[8];
-                    unpack8(r_old[c], old);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) old[e] += m[c * 8 + e];
-                    *reinterpret_cast<uint4*>(dst + c * 8) = pack8(old);
-                }
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(smem + OFF_RT + t * 128 + (((hsel * 4 + c) ^ (t & 7)) << 4)) = pack8(&m[c * 8]);
             }
         }
         tc::fence_async_smem();   // the result tiles are read by bulk copies
@@ -612,8 +607,8 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
     const void* bases[6] = {w, r, k, v, a, b};   // maps[m]: the six streams as [B*T tokens][H*64 channels]
     if (!make_stream_maps(&maps, bases, 6, B, T, H)) return B200WKV_ELAUNCH;
     StreamMaps out_maps;                         // m[0]: the outputs, with the 128-byte swizzle of the kernel's output tile
-    const void* out_bases[1] = {y};
-    if (!make_stream_maps(&out_maps, out_bases, 1, B, T, H, /*swizzle128=*/true)) return B200WKV_ELAUNCH;
+    const void* out_bases[2] = {y, residual ? (const void*)((char*)residual + lay.rbar) : y};   // m[1]: the R- rows
+    if (!make_stream_maps(&out_maps, out_bases, 2, B, T, H, /*swizzle128=*/true)) return B200WKV_ELAUNCH;
     // Without a residual (inference) and with fewer sequences than CTA slots, every sequence is offered to several
     // CTAs, which cut it at start flags where there are any (see the kernel): at most 8 pieces of at least 128 tokens.
     int pieces = 1;
@@ -629,7 +624,7 @@ int wkv7_chunk_fwd(cudaStream_t st, int B, int T, int H, const void* w, const vo
                                                           (const bf*)a, (const bf*)b, (const bf*)s0, length, ns,
                                                           (bf*)y, (bf*)s_out, (float*)residual,
                                                           residual ? (float*)residual + (size_t)B * H * ((T + kC - 1) / kC) * kN * kN : nullptr,
-                                                          maps, out_maps.m[0],
+                                                          maps, out_maps.m[0], out_maps.m[1],
                                                           residual ? (unsigned char*)((float*)residual + chunk_saved_offset_floats(B, T, H)) : nullptr,
                                                           *range_flag, *range_ticket, residual_mark,
                                                           residual ? (bf*)((char*)residual + lay.mprime) : nullptr,
