@@ -53,13 +53,19 @@ constexpr int OFF_CUMF = OFF_W;             // fp32 cumulative log2-decay while 
 constexpr int OFF_LF = OFF_W;               // last epilogue: fp32 r dr - k dk per token, then D_{t-1} (16 KB, swizzled rows)
 constexpr int OFF_P3 = OFF_W + T128;        // last epilogue: fp32 a da (16 KB, swizzled rows)
 constexpr int OFF_UB = OFF_X1;              // last epilogue: fp32 a da - b db (16 KB over X1 | X2, swizzled rows)
-constexpr int OFF_SEG = OFF_STG + 7 * T64;  // last epilogue: per-16-token totals of the decay-gradient scan, [4][64] floats, in the
-                                            // tail of the [dY ; dG] slab that the next block's staging tiles do not reach
+// Gradient tiles on their way out: [64 tokens][128 bytes] with the 128-byte swizzle of the tiled copies (piece index
+// XOR token mod 8).  dk, db, dr, da are written by the last epilogue over [V ; sa] and [dY ; dG], whose products are
+// done, and must have been read before the next block's staging tiles 4..6 land on them; dv, and at the very end of
+// the block the decay gradient, use the 8 KB that only the last epilogue's fp32 buffer shares.
+constexpr int OFF_TK = OFF_VSA, OFF_TB = OFF_VSA + T64, OFF_TR = OFF_DD, OFF_TA = OFF_DD + T64;
+constexpr int OFF_TV = OFF_X2;
 struct Small {
-    float lam[kN];       // 2^(block total)
-    float d_end[kN];     // D at the block end
     uint64_t bar[8];     // 0..3 product rounds, 4 staging, 5 P_rb|P_rk|sa, 6 T|A_ak, 7 S0
     uint32_t tmem;
+    uint32_t pad[3];
+    float lam[kN];       // 2^(block total)
+    float d_end[kN];     // D at the block end
+    float seg_tail[kN];  // with lam and d_end (both dead by then): per-16-token totals of the decay-gradient scan, [3][64]
 };
 constexpr int SMEM_BYTES = OFF_SMALL + 1024;
 static_assert(sizeof(Small) <= 1024, "small state must fit its kilobyte");
@@ -112,7 +118,7 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
                      __nv_bfloat16* __restrict__ dw, __nv_bfloat16* __restrict__ dr, __nv_bfloat16* __restrict__ dk,
                      __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ da, __nv_bfloat16* __restrict__ db,
                      int* __restrict__ status, int has_dy, unsigned char* __restrict__ fscr_all,
-                     const __grid_constant__ StreamMaps maps) {
+                     const __grid_constant__ StreamMaps maps, const __grid_constant__ StreamMaps out_maps) {
     if (*residual_mark != 0) return;            // the forward fell back to the sequential kernels
     extern __shared__ __align__(1024) unsigned char smem[];
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
@@ -121,7 +127,6 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
     const int row = quad * 32 + lane;                // TMEM lane == tile row
     const int nBlk = Tlen / kC;
     const int n_items = BH * nBlk;   // (the launcher refuses shapes whose block count overflows an int)
-    const size_t tok_stride = (size_t)H * kN;
     unsigned char* const fscr = fscr_all + (size_t)blockIdx.x * 4 * GTILE;
     // the 128-byte swizzle of the staging tiles is a function of the shared-memory address
     if ((tc::smem_u32(smem) & 1023u) != 0) {
@@ -166,7 +171,8 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
     float* lf = reinterpret_cast<float*>(smem + OFF_LF);
     float* p3buf = reinterpret_cast<float*>(smem + OFF_P3);
     float* ubuf = reinterpret_cast<float*>(smem + OFF_UB);
-    float* seg = reinterpret_cast<float*>(smem + OFF_SEG);
+    float* seg = sm.lam;   // [3][64]: totals of segments 1..3 (see Small)
+    enum { OUT_W = 0, OUT_R = 1, OUT_K = 2, OUT_V = 3, OUT_A = 4, OUT_B = 5 };   // tensor maps of the gradients
     uint32_t par = 0;   // every barrier completes one phase per block
 
     // scaling role: one token, two column blocks (16 channels)
@@ -175,18 +181,21 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
     const int si = tid & 63, sc = (tid >> 6) * 2;
 
     const int n_streams = has_dy ? 7 : 6;
-    auto issue_stage = [&](int it) {
+    // raw tiles m_from..m_to-1 of block `it` (thread kStageThread; the first call of a block announces all of them)
+    auto issue_stage = [&](int it, int m_from, int m_to) {
         if (tid == kStageThread) {
             const int bh_ = it / nBlk, blk_ = it % nBlk;
-            tc::mbar_expect_tx(&sm.bar[4], (uint32_t)(n_streams * T64));
+            if (m_from == 0) tc::mbar_expect_tx(&sm.bar[4], (uint32_t)(n_streams * T64));
             const int x = (bh_ % H) * kN, y = (bh_ / H) * Tlen + blk_ * kC;
 #pragma unroll
             for (int m = 0; m < 7; ++m)
-                if (m < n_streams) tc::tensor_load_2d(smem + OFF_STG + m * T64, &maps.m[m], x, y, &sm.bar[4]);
+                if (m >= m_from && m < m_to && m < n_streams) tc::tensor_load_2d(smem + OFF_STG + m * T64, &maps.m[m], x, y, &sm.bar[4]);
         }
     };
     tc::fence_async_smem();
-    issue_stage(item);
+    issue_stage(item, 0, 7);
+    bool pend_dw = false;    // the decay-gradient tile of the previous block waits for a CTA barrier
+    int pend_x = 0, pend_y = 0;
     // what the loop needs to know about a block before it touches it, fetched one block ahead
     int meta_L = min((int)length[(item / nBlk) / H], Tlen);
     bool meta_reset = new_starts[(size_t)((item / nBlk) / H) * Tlen + (item % nBlk) * kC] != 0;
@@ -196,7 +205,6 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
         const int L = meta_L;
         const bool reset_here = meta_reset;
         const int p = blk * kC, p1 = p + kC;
-        const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)(bh % H) * kN;
         const size_t st_base = (size_t)bh * kN * kN;
         const unsigned char* tiles = saved + ((size_t)bh * nBlk + blk) * kSavedBytes;
         const __nv_bfloat16* dsg = ds_state + ((size_t)bh * nBlk + blk) * kN * kN;
@@ -215,6 +223,10 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
                                              : make_uint4(0, 0, 0, 0);
         tc::fence_async_smem();
         __syncthreads();   // the staging tiles are empty; the previous block's last epilogue has finished everywhere
+        if (issuer_b && pend_dw) {
+            tc::tensor_store_2d(&out_maps.m[OUT_W], pend_x, pend_y, smem + OFF_TV);
+            tc::bulk_commit();
+        }
         // P_rb | P_rk and sa of this block (their hosts are free now); T | A_ak follow once the scan buffer is done with
         if (warp == kSavedWarp) {
             if (lane == 0) tc::mbar_expect_tx(&sm.bar[5], (uint32_t)(3 * T64));
@@ -388,6 +400,7 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
 #pragma unroll
             for (int c = 0; c < 4; ++c) slab_store(smem + OFF_DD, P128, 64 + row, hsel * 4 + c, pack8(&z[c * 8]));
         }
+        if (issuer_b) tc::bulk_wait_read<0>();   // the previous block's decay-gradient tile has left: dV takes its place
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
@@ -448,9 +461,9 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
             float x[32];
             tc::tmem_ld32(lane_addr + T_GD + hsel * 32, x);
             tc::tmem_wait_ld();
-            __nv_bfloat16* dst = dv + seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&x[c * 8]);
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(smem + OFF_TV + t * 128 + (((hsel * 4 + c) ^ (t & 7)) << 4)) = pack8(&x[c * 8]);
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
@@ -463,10 +476,13 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
             tc::commit(&sm.bar[3]);
         } else if (issuer_b) {
             tc::fence_after_sync();
+            tc::tensor_store_2d(&out_maps.m[OUT_V], (bh % H) * kN, bi * Tlen + p, smem + OFF_TV);
+            tc::bulk_commit();
             mma_k64(tbase + T_RA, mnmaj128u(sWY + HALF), mnmaj128u(sBK), ID_MM, false);
             mma_k64(tbase + T_RA, mnmaj128u(sWY), mnmaj128u(sBK + HALF), ID_MM, true);
             if (!tc::mbar_wait(&sm.bar[7], par)) failed = true;   // S0 has landed
             mma_k64(tbase + T_RA, kmaj128u(sDD), mnmaj64u(sX1), ID_KM, true);
+            tc::bulk_wait_read<0>();   // the dV tile has left before this round is reported done: the last epilogue writes over it
             tc::commit(&sm.bar[3]);
         }
         // ---- while the products run: this row's decay factors from the scratch
@@ -481,7 +497,8 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
         if (!tc::mbar_wait(&sm.bar[3], par)) failed = true;
         tc::fence_after_sync();
         // ================= last epilogue: unscale, write dk db dr da, decay gradient =================
-        const size_t gtok = seq_base + (size_t)(p + t) * tok_stride + hsel * 32;
+        unsigned char* const tile_x = smem + ((row < 64) ? OFF_TK : OFF_TB) + t * 128;   // dk | db
+        unsigned char* const tile_z = smem + ((row < 64) ? OFF_TR : OFF_TA) + t * 128;   // dr | da
         float* const ubase = (row < 64) ? lf : ubuf;   // r dr - k dk of the token | a da - b db of the token
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -506,10 +523,9 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
                     *reinterpret_cast<float4*>(&p3buf[swz4(t, cb * 2)]) = make_float4(pz[0], pz[1], pz[2], pz[3]);
                     *reinterpret_cast<float4*>(&p3buf[swz4(t, cb * 2 + 1)]) = make_float4(pz[4], pz[5], pz[6], pz[7]);
                 }
-                __nv_bfloat16* dx = (row < 64) ? dk : db;
-                __nv_bfloat16* dz = (row < 64) ? dr : da;
-                *reinterpret_cast<uint4*>(dx + gtok + c * 8) = mul8(pack8(&x[h2 * 8]), fxr[c]);
-                *reinterpret_cast<uint4*>(dz + gtok + c * 8) = mul8(pack8(&z[h2 * 8]), fzr[c]);
+                const int piece = ((cb ^ (t & 7)) << 4);
+                *reinterpret_cast<uint4*>(tile_x + piece) = mul8(pack8(&x[h2 * 8]), fxr[c]);
+                *reinterpret_cast<uint4*>(tile_z + piece) = mul8(pack8(&z[h2 * 8]), fzr[c]);
             }
         }
         // log-decay of this token (rows 64..127 write the decay gradient): asked for ahead of the scan
@@ -518,9 +534,21 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
 #pragma unroll
             for (int c = 0; c < 4; ++c) lgr[c] = *reinterpret_cast<const uint4*>(fscr + F_LOGW * GTILE + (hsel * 4 + c) * GCB + t * 16);
         }
+        const float d_end_c = sm.d_end[tid & 63];   // (its storage serves the scan below)
+        tc::fence_async_smem();   // the gradient tiles are read by bulk copies
         tc::fence_before_sync();
         __syncthreads();   // every operand slab has been read for the last time: the next block's rows may arrive
-        if (item_next < n_items) issue_stage(item_next);
+        if (tid == kStageThread) {
+            const int x = (bh % H) * kN, y = bi * Tlen + p;
+            tc::tensor_store_2d(&out_maps.m[OUT_K], x, y, smem + OFF_TK);
+            tc::tensor_store_2d(&out_maps.m[OUT_B], x, y, smem + OFF_TB);
+            tc::tensor_store_2d(&out_maps.m[OUT_R], x, y, smem + OFF_TR);
+            tc::tensor_store_2d(&out_maps.m[OUT_A], x, y, smem + OFF_TA);
+            tc::bulk_commit();
+        }
+        if (item_next < n_items) issue_stage(item_next, 0, 4);   // tiles 0..3 land on [A~;R~], [B~;K~]
+        if (tid == kStageThread) tc::bulk_wait_read<0>();        // tiles 4..6 on the gradient tiles, once those are read
+        if (item_next < n_items) issue_stage(item_next, 4, 7);
         {   // D_{t-1} = D_t + u_t from D at the block end: suffix sums over 4 segments of 16 tokens, all loads first
             const int c = tid & 63, sg = tid >> 6;
             float vv[16];
@@ -528,10 +556,10 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
             for (int tt = 0; tt < 16; ++tt) vv[tt] = lf[swz1(sg * 16 + tt, c)] + ubuf[swz1(sg * 16 + tt, c)];
 #pragma unroll
             for (int tt = 14; tt >= 0; --tt) vv[tt] += vv[tt + 1];
-            seg[sg * 64 + c] = vv[0];
+            if (sg > 0) seg[(sg - 1) * 64 + c] = vv[0];
             __syncthreads();
-            float off = sm.d_end[c];
-            for (int s2 = 3; s2 > sg; --s2) off += seg[s2 * 64 + c];
+            float off = d_end_c;
+            for (int s2 = 3; s2 > sg; --s2) off += seg[(s2 - 1) * 64 + c];
 #pragma unroll
             for (int tt = 0; tt < 16; ++tt) lf[swz1(sg * 16 + tt, c)] = vv[tt] + off;
         }
@@ -554,11 +582,14 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
 #pragma unroll
                 for (int e = 0; e < 32; ++e) o[e] = 0.f;
             }
-            __nv_bfloat16* dst = dw + gtok;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(&o[c * 8]);
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(smem + OFF_TV + t * 128 + (((hsel * 4 + c) ^ (t & 7)) << 4)) = pack8(&o[c * 8]);
         }
-        tc::fence_async_smem();   // the scan buffers are rewritten by bulk copies early in the next block
+        pend_dw = true;
+        pend_x = (bh % H) * kN;
+        pend_y = bi * Tlen + p;
+        tc::fence_async_smem();   // the scan buffers are rewritten by bulk copies early in the next block; the tile is read by one
         tc::fence_before_sync();
         par ^= 1u;
         item = item_next;
@@ -566,6 +597,14 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
     if (failed && status != nullptr) atomicExch(status, 2);
     tc::fence_before_sync();
     __syncthreads();
+    if (issuer_b) {
+        if (pend_dw) {
+            tc::tensor_store_2d(&out_maps.m[OUT_W], pend_x, pend_y, smem + OFF_TV);
+            tc::bulk_commit();
+        }
+        tc::bulk_wait_all<0>();   // shared memory stays this CTA's until every tile has been read
+    }
+    if (tid == kStageThread) tc::bulk_wait_all<0>();
     if (warp == 0) tc::tmem_dealloc(tbase, 256);
 }
 
@@ -588,6 +627,9 @@ int wkv7_grad_bwd(cudaStream_t st, int B, int T, int H, const void* w, const voi
     StreamMaps maps;
     const void* bases[7] = {w, r, k, v, a, b, dy};
     if (!make_stream_maps(&maps, bases, dy != nullptr ? 7 : 6, B, T, H, /*swizzle128=*/true)) return B200WKV_ELAUNCH;
+    StreamMaps out_maps;
+    const void* out_bases[6] = {dw, dr, dk, dv, da, db};
+    if (!make_stream_maps(&out_maps, out_bases, 6, B, T, H, /*swizzle128=*/true)) return B200WKV_ELAUNCH;
     const long long items = (long long)BH * nBlk;
     if (items > 2147483647LL) return B200WKV_ESHAPE;
     long long slots = 2LL * sm_count_of_current_device();
@@ -596,7 +638,7 @@ int wkv7_grad_bwd(cudaStream_t st, int B, int T, int H, const void* w, const voi
     wkv7_grad_bwd_kernel<<<grid, 256, SMEM_BYTES, st>>>(T, H, BH, length, ns, (const bf*)(base + lay.dstate), s_at_len, saved,
                                                         (const int*)(base + lay.fast), residual_mark, (bf*)dw, (bf*)dr, (bf*)dk,
                                                         (bf*)dv, (bf*)da, (bf*)db, wkv7_chunk_status_word(), dy != nullptr ? 1 : 0,
-                                                        (unsigned char*)(base + lay.fscr), maps);
+                                                        (unsigned char*)(base + lay.fscr), maps, out_maps);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 
