@@ -45,7 +45,7 @@ inline size_t chunk_saved_offset_floats(int B, int T, int H) {
 //                                   (8 column blocks of [64 rows][16 bytes], like the saved tiles)
 //   [B*T][H*64]               bf16  R- = R~ + P_rb W~ (token rows, laid out like the streams): y_t = R-_t S0^T + ...
 //   [B*H][ceil(T/64)][64]     fp32  L_C, the decay over the whole block
-//   [B*H][ceil(T/64)][64][64] bf16  scratch of the backward: the state gradient leaving every block
+//   [B*H][ceil(T/64)][64][64] bf16  scratch of the backward: the state gradient leaving every block (column blocks, as M')
 //   [B*H]                     int   1 if the forward walked the whole sequence as full, saved blocks
 //   [kGradCtas][4][64][64]    bf16  scratch of the gradient kernel, one set per CTA: the decay factors 1/L_t, L_t,
 //                                   L_{t-1} and the log-decay of the block in hand (written when the operands are

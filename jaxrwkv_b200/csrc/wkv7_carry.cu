@@ -132,8 +132,9 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
                 const uint32_t lo = pack2(acc[nt][0], acc[nt][1]), hi = pack2(acc[nt][2], acc[nt][3]);
-                *reinterpret_cast<uint32_t*>(out + (size_t)(i0 + g) * kN + nt * 8 + 2 * q) = lo;
-                *reinterpret_cast<uint32_t*>(out + (size_t)(i0 + g + 8) * kN + nt * 8 + 2 * q) = hi;
+                // (8 column blocks of [64 rows][8]: eight lanes' rows are one 128-byte line)
+                *reinterpret_cast<uint32_t*>(out + nt * (kN * 8) + (i0 + g) * 8 + 2 * q) = lo;
+                *reinterpret_cast<uint32_t*>(out + nt * (kN * 8) + (i0 + g + 8) * 8 + 2 * q) = hi;
                 afrag[nt >> 1][(nt & 1) * 2] = lo;
                 afrag[nt >> 1][(nt & 1) * 2 + 1] = hi;
             }

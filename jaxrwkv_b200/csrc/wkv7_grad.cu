@@ -210,8 +210,8 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
         const __nv_bfloat16* dsg = ds_state + ((size_t)bh * nBlk + blk) * kN * kN;
 
         // the state gradient leaving this block (global memory) is asked for before anything waits
-        const uint4 ds_raw0 = *reinterpret_cast<const uint4*>(dsg + si * kN + sc * 8);
-        const uint4 ds_raw1 = *reinterpret_cast<const uint4*>(dsg + si * kN + (sc + 1) * 8);
+        const uint4 ds_raw0 = *reinterpret_cast<const uint4*>(dsg + sc * (kN * 8) + si * 8);         // column block sc, row si
+        const uint4 ds_raw1 = *reinterpret_cast<const uint4*>(dsg + (sc + 1) * (kN * 8) + si * 8);
         // ================= raw rows out of the staging tiles (registers) =================
         uint4 raw[7][2];   // w r k v a b dy ; column blocks st_jb, st_jb + 1
         if (!tc::mbar_wait(&sm.bar[4], par)) failed = true;
