@@ -102,7 +102,10 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                       int* __restrict__ fast_flag, int pieces) {
     extern __shared__ __align__(1024) unsigned char smem[];   // (the swizzle of the output tile is a function of the address)
     Small& sm = *reinterpret_cast<Small*>(smem + OFF_SMALL);
-    const int bh = blockIdx.x / pieces, piece = blockIdx.x % pieces, bi = bh / H, h = bh % H;
+    // (all first pieces come first in the grid: where no cut exists the other pieces' CTAs return at once, and the
+    // CTAs that do the work are then spread over the SMs before any SM takes a second one)
+    const int n_seq = (int)gridDim.x / pieces;
+    const int bh = blockIdx.x % n_seq, piece = blockIdx.x / n_seq, bi = bh / H, h = bh % H;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = warp & 3, hsel = warp >> 2;
     const int row = quad * 32 + lane;
