@@ -138,12 +138,13 @@ __device__ __forceinline__ void slab_store(unsigned char* slab, int cb, int row,
 }
 
 
-// One warp: C(16x8) = A(16xK) B(Kx8), all fp32 row-major in shared memory, K a multiple of 8.
+// One warp: C(16x8) = A(16xK) B(Kx8), all fp32 row-major in shared memory; only k in [k_from, k_to) (multiples
+// of 8) is walked, for operands that are known to be zero outside that range.
 __device__ __forceinline__ void tile_mma_tf32(const float* A, int lda, const float* B, int ldb, float* C, int ldc,
-                                              int K, int lane) {
+                                              int k_from, int k_to, int lane) {
     const int g = lane >> 2, t = lane & 3;
     float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
-    for (int k0 = 0; k0 < K; k0 += 8) {
+    for (int k0 = k_from; k0 < k_to; k0 += 8) {
         const uint32_t a0 = __float_as_uint(A[g * lda + k0 + t]), a1 = __float_as_uint(A[(g + 8) * lda + k0 + t]);
         const uint32_t a2 = __float_as_uint(A[g * lda + k0 + t + 4]), a3 = __float_as_uint(A[(g + 8) * lda + k0 + t + 4]);
         const uint32_t b0 = __float_as_uint(B[(k0 + t) * ldb + g]), b1 = __float_as_uint(B[(k0 + t + 4) * ldb + g]);
@@ -183,12 +184,13 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
         float x[16];
 #pragma unroll
         for (int t = 0; t < 16; ++t) x[t] = 0.f;
-        // L is strictly lower and x[m] is still zero for m >= t, so every row is a full 16-long dot
-        // product: four vector loads per row that do not depend on x and can be issued ahead
+        // L is strictly lower: row t needs its first t entries only (whole groups of four are loaded or left out;
+        // x[m] is still zero for m >= t).  The loads do not depend on x and can be issued ahead.
 #pragma unroll
         for (int t = 0; t < 16; ++t) {
             const float4* lr = reinterpret_cast<const float4*>(&L[(o + t) * LF_PITCH + o]);
-            const float4 l0 = lr[0], l1 = lr[1], l2 = lr[2], l3 = lr[3];
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 l0 = (t > 0) ? lr[0] : zero4, l1 = (t > 4) ? lr[1] : zero4, l2 = (t > 8) ? lr[2] : zero4, l3 = (t > 12) ? lr[3] : zero4;
             float a0 = (t == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
             a0 = fmaf(l0.x, x[0], a0); a1 = fmaf(l0.y, x[1], a1); a2 = fmaf(l0.z, x[2], a2); a3 = fmaf(l0.w, x[3], a3);
             a0 = fmaf(l1.x, x[4], a0); a1 = fmaf(l1.y, x[5], a1); a2 = fmaf(l1.z, x[6], a2); a3 = fmaf(l1.w, x[7], a3);
@@ -214,11 +216,12 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
     if (warp < 4) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int q = warp >> 1, n0 = (warp & 1) * 8, o = q * 32;
+        // (X11 is lower triangular: its rows above n0 are zero in this column tile)
         tile_mma_tf32(L + (o + 16) * LF_PITCH + o, LF_PITCH, X + o * LF_PITCH + o + n0, LF_PITCH,
-                      scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH, 16, lane);
+                      scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH, n0, 16, lane);
         asm volatile("bar.sync 1, 128;" ::: "memory");
         tile_mma_tf32(X + (o + 16) * LF_PITCH + o + 16, LF_PITCH, scr + (q * 16) * TRI_SCR_PITCH + n0, TRI_SCR_PITCH,
-                      X + (o + 16) * LF_PITCH + o + n0, LF_PITCH, 16, lane);
+                      X + (o + 16) * LF_PITCH + o + n0, LF_PITCH, 0, 16, lane);
     }
     __syncthreads();
     // 32 -> 64: W = L21 X11 (32x32x32 = eight tiles), then X21 = X22 W
@@ -226,10 +229,11 @@ __device__ __forceinline__ void tri_inverse_64(const float* __restrict__ L, floa
     {
         const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 8;
         tile_mma_tf32(L + (32 + m0) * LF_PITCH, LF_PITCH, X + n0, LF_PITCH, scr + m0 * TRI_SCR_PITCH + n0, TRI_SCR_PITCH,
-                      32, lane);
+                      n0, 32, lane);
         __syncthreads();
+        // (X22 is lower triangular: the rows of this tile end at column m0 + 15)
         tile_mma_tf32(X + (32 + m0) * LF_PITCH + 32, LF_PITCH, scr + n0, TRI_SCR_PITCH, X + (32 + m0) * LF_PITCH + n0,
-                      LF_PITCH, 32, lane);
+                      LF_PITCH, 0, m0 + 16, lane);
     }
     before_last_barrier();
     __syncthreads();

@@ -66,9 +66,10 @@ constexpr int STG_TILE = kC * kN * 2;
 static_assert(5 * STG_TILE <= 2 * SLAB128 + SLAB64 && STG_TILE <= SLAB128 - SLAB64, "staging tiles must fit their hosts");
 __device__ __forceinline__ int stage_off(int m) { return m < 5 ? OFF_AR + m * STG_TILE : OFF_M2A + SLAB64; }
 struct Small {
-    float h1[kN];        // cumulative log-decay of tokens 0..31
+    float h1[kN];        // cumulative log-decay of tokens 0..31, stored [e][jb] for channel 8 jb + e
     float tot[kN];       // ... of the whole chunk
     float lam[kN];       // exp(tot)
+    float lamt[kN];      // the same, stored [e][jb]
     uint64_t bar[5];   // 0..3 product rounds, 4 staging tiles
     uint32_t nsm[2];
     uint32_t tmem;
@@ -291,8 +292,10 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
 #pragma unroll
                 for (int e = 0; e < 8; ++e) lw[q][e] = 0.f;
             }
-            *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
-            *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 8 + 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
+            // (column 4 jb + e holds channel 8 jb + e, column 32 + 4 jb + e channel 8 jb + 4 + e: the eight lanes of a
+            // token then write, and later read, 128 contiguous bytes)
+            *reinterpret_cast<float4*>(&cum[t * LF_PITCH + jb * 4]) = make_float4(lw[q][0], lw[q][1], lw[q][2], lw[q][3]);
+            *reinterpret_cast<float4*>(&cum[t * LF_PITCH + 32 + jb * 4]) = make_float4(lw[q][4], lw[q][5], lw[q][6], lw[q][7]);
         }
         __syncthreads();
         if (tid < 128) {   // inclusive scan over tokens, two independent halves of 32 per channel
@@ -304,19 +307,23 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
                 run += cum[t * LF_PITCH + j];
                 cum[t * LF_PITCH + j] = run;
             }
-            if (half == 0) sm.h1[j] = run;
-            else sm.tot[j] = run;   // second-half sum for now
+            // column j of the scan buffer is channel ch = 8 jb + e
+            const int cjb = (j & 31) >> 2, ce = (j & 3) + ((j >> 5) << 2), ch = cjb * 8 + ce;
+            if (half == 0) sm.h1[ce * 8 + cjb] = run;
+            else sm.tot[ch] = run;   // second-half sum for now
         }
         __syncthreads();
         if (tid < 64) {
-            const float total = sm.h1[tid] + sm.tot[tid];
+            const float total = sm.h1[(tid & 7) * 8 + (tid >> 3)] + sm.tot[tid];
             // A decay so strong that 1 / L leaves the range the products can carry (never reached by decays
             // of the model's own parametrisation): the chunked form cannot represent this chunk.  Record it;
             // the token-sequential kernel launched behind this one redoes the call when it finds the mark.
             if (total < kCumFloor) atomicExch(range_flag, range_ticket);
             const float t2 = fmaxf(total, kCumFloor);
             sm.tot[tid] = t2;
-            sm.lam[tid] = ex2(t2);
+            const float lam_c = ex2(t2);
+            sm.lam[tid] = lam_c;
+            sm.lamt[(tid & 7) * 8 + (tid >> 3)] = lam_c;
         }
         if (warp == 7) tc::bulk_wait_read<0>();   // the result tiles have left the slabs that are written next
         __syncthreads();
@@ -324,13 +331,13 @@ wkv7_chunk_fwd_kernel(int Tlen, int H, const __nv_bfloat16* __restrict__ w, cons
         {
             float h1v[8], lamv[8];   // first-half totals; 2^(chunk total) per channel
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { h1v[e] = sm.h1[jb * 8 + e]; lamv[e] = sm.lam[jb * 8 + e]; }
+            for (int e = 0; e < 8; ++e) { h1v[e] = sm.h1[e * 8 + jb]; lamv[e] = sm.lamt[e * 8 + jb]; }
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int t = q * 32 + tsub;
                 float c[8];
-                *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8]);
-                *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 8 + 4]);
+                *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + jb * 4]);
+                *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cum[t * LF_PITCH + 32 + jb * 4]);
                 float eL[8], eI[8], eP[8], eE[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {

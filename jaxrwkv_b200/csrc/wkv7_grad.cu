@@ -331,14 +331,14 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
             mma_k64(tbase + T_GD, mnmaj64u(sPRB), mnmaj128u(sDD), ID_MM, true);
             tc::commit(&sm.bar[0]);
         }
-        if (quad == 3) {
-            // D at the block end, by the two warps that have no part in the next two rounds:
+        if (quad >= 2) {
+            // D at the block end, by the four warps that have no part in the next two epilogues:
             //   D_end[c] = sum_i dS[i][c] S_end[i][c] = (sum_i dSL[i][c] S_end[i][c]) / L_C[c]
             // with dSL read from its slab.  S_end is the state at `length` when the block ends there, else the
             // entering state the forward saved for the next block (zero behind a start flag, where dS is too).
-            // Thread (column block cbk, row group ig) adds rows ig, ig + 8, ...; the eight row groups of a column
-            // block sit in one quarter of a warp and meet in a butterfly of fixed order.
-            const int a_tid = hsel * 32 + lane, cbk = a_tid >> 3, ig = a_tid & 7;
+            // Thread (column block cbk, row group ig) adds rows ig, ig + 16, ...; the sixteen row groups of a column
+            // block sit in one half of a warp and meet in a butterfly of fixed order.
+            const int a_tid = ((quad - 2) * 2 + hsel) * 32 + lane, cbk = a_tid >> 4, ig = a_tid & 15;
             float acc[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] = 0.f;
@@ -347,8 +347,8 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
                 const float* sf = s_at_len + st_base + cbk * 8;
                 const unsigned char* sb = tiles + kSavedBytes + SAVED_S0 * GTILE + cbk * GCB;
 #pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                    const int i = ig + 8 * m;
+                for (int m = 0; m < 4; ++m) {
+                    const int i = ig + 16 * m;
                     float se[8], dsl[8];
                     if (at_len) {
                         const float4 s0 = __ldg(reinterpret_cast<const float4*>(sf + i * kN)), s1 = __ldg(reinterpret_cast<const float4*>(sf + i * kN + 4));
@@ -366,6 +366,7 @@ wkv7_grad_bwd_kernel(int Tlen, int H, int BH, const uint32_t* __restrict__ lengt
                 acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
                 acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
                 acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 4);
+                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
             }
             if (ig == 0) {
 #pragma unroll
