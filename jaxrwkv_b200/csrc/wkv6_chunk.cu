@@ -361,12 +361,15 @@ struct BwdStage {
     bf r[kC6][PITCH], k[kC6][PITCH], v[kC6][PITCH], w[kC6][PITCH], dy[kC6][PITCH];
     bf s0[kN][PITCH];          // S0^T[j][i]; once the products have read it, r dr' and k dk' per token and channel (fp32)
 };
-static_assert(sizeof(bf) * kN * PITCH >= 2 * sizeof(float) * kC6 * kN, "the two fp32 tiles must fit over the state tile");
+// fp32 [token][channel] tiles that the epilogue's threads address as (row g, column pair 2 q): with 72 floats per row the
+// sixteen lanes of a 64-bit access (four rows, four column pairs) fall into 32 different banks
+constexpr int EPITCH = 72;
+static_assert(sizeof(bf) * kN * PITCH >= 2 * sizeof(float) * kC6 * EPITCH, "the two fp32 tiles must fit over the state tile");
 struct Bwd6cSmem {
     BwdStage st[2];
     bf ops[4][kC6][PITCH];     // R~, K~, R0, K^ while the products run; then dr, dk, dv, dw on their way out
     bf ds[kN][PITCH];          // dS_C^T[j][i] in bf16, for the one product that contracts over j
-    float e2[kC6][kN], e3[kC6][kN];   // exp(c_{t-1} - c_m) and exp(c_m - c_t): what turns dR~, dK~ into dr, dk
+    float e2[kC6][EPITCH], e3[kC6][EPITCH];   // exp(c_{t-1} - c_m) and exp(c_m - c_t): what turns dR~, dK~ into dr, dk
     float em[kN], ecm[kN];     // exp(c_m) and exp(c_C - c_m): the same for dR0 and dK^
     float tot[2][kN];
     float wc[kN];              // exp(c_C), or 0 when a start flag lies in the chunk
@@ -684,8 +687,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         }
         __syncthreads();                                              // S4: nobody reads the operand tiles any more
         // ---- epilogue: rows t = g, g + 8; column pairs i = j0 + 8 nt + 2 q, + 1
-        float (*ea)[kN] = reinterpret_cast<float (*)[kN]>(sm.st[stage].s0);
-        float (*eb)[kN] = ea + kC6;
+        float (*ea)[EPITCH] = reinterpret_cast<float (*)[EPITCH]>(sm.st[stage].s0);
+        float (*eb)[EPITCH] = ea + kC6;
         {
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
