@@ -116,7 +116,7 @@ struct Fwd6cSmem {
     uint8_t ns[kStages6][kC6];
 };
 
-// One CTA of 128 threads per (batch, head).  ckpt: the state entering every chunk, bf16 [value j][key i], for
+// One CTA of 128 threads per (batch, head).  ckpt: the state entering every chunk, bf16 S^T[value j][key i] in 8 column blocks of [64 j][8 i], for
 // the backward (may be NULL).  The kernel gives up (flag := ticket, see the file header) on a decay above 1 and on a
 // half-chunk decay beyond exp(-80).
 __global__ void __launch_bounds__(128, 4)
@@ -217,8 +217,9 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             bf* dst = ckpt + ((size_t)bh * (nC + 1) + (part == 0 ? c : nC)) * kN * kN;
 #pragma unroll
             for (int ni = 0; ni < 8; ++ni) {
-                *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g) * kN + 8 * ni + 2 * q) = pack2(acc[ni][0], acc[ni][1]);
-                *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g + 8) * kN + 8 * ni + 2 * q) = pack2(acc[ni][2], acc[ni][3]);
+                // (8 column blocks of [64 rows j][8 keys i]: the eight row groups of a warp write one 128-byte line)
+                *reinterpret_cast<uint32_t*>(dst + ni * (kN * 8) + (j0 + g) * 8 + 2 * q) = pack2(acc[ni][0], acc[ni][1]);
+                *reinterpret_cast<uint32_t*>(dst + ni * (kN * 8) + (j0 + g + 8) * 8 + 2 * q) = pack2(acc[ni][2], acc[ni][3]);
             }
         }
         // ---- phase A: cumulative log-decay and scaled operands
@@ -359,12 +360,16 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 // token-by-channel results and 16 value rows of dS^T, and computes the 16x16 score blocks for itself.
 struct BwdStage {
     bf r[kC6][PITCH], k[kC6][PITCH], v[kC6][PITCH], w[kC6][PITCH], dy[kC6][PITCH];
-    bf s0[kN][PITCH];          // S0^T[j][i]; once the products have read it, r dr' and k dk' per token and channel (fp32)
+    // S0^T[j][i] as it lies in the residual: 8 column blocks of [64 rows j][8 keys i] (a linear copy; the eight rows of an
+    // ldmatrix tile are 128 contiguous bytes); once the products have read it, r dr' and k dk' per token and channel
+    // (fp32, two tiles of [16][EPITCH], which need the tail)
+    bf s0[8][kN][8];
+    bf s0_tail[kN * PITCH - 8 * kN * 8];
 };
 // fp32 [token][channel] tiles that the epilogue's threads address as (row g, column pair 2 q): with 72 floats per row the
 // sixteen lanes of a 64-bit access (four rows, four column pairs) fall into 32 different banks
 constexpr int EPITCH = 72;
-static_assert(sizeof(bf) * kN * PITCH >= 2 * sizeof(float) * kC6 * EPITCH, "the two fp32 tiles must fit over the state tile");
+static_assert(sizeof(bf) * kN * PITCH >= 2 * sizeof(float) * kC6 * EPITCH, "the two fp32 tiles must fit over the state tile and its tail");
 struct Bwd6cSmem {
     BwdStage st[2];
     bf ops[4][kC6][PITCH];     // R~, K~, R0, K^ while the products run; then dr, dk, dv, dw on their way out
@@ -446,7 +451,10 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             cp_async16_zfill(&st.dy[srow][spiece], dy != nullptr ? dy + off : r + off, ok && dy != nullptr);
             const bf* src = ckpt + ((size_t)bh * (nC + 1) + c) * kN * kN;
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) cp_async16_zfill(&st.s0[srow + 16 * rr][spiece], src + (size_t)(srow + 16 * rr) * kN + spiece, true);
+            for (int rr = 0; rr < 4; ++rr) {   // piece tid + 128 rr of the tile: row = piece mod 64 of column block piece / 64
+                const int pc = tid + 128 * rr;
+                cp_async16_zfill(&st.s0[pc >> 6][pc & 63][0], src + (size_t)pc * 8, true);
+            }
         }
         cp_async_commit();
     };
@@ -455,7 +463,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         const bf* src = ckpt + ((size_t)bh * (nC + 1) + slot) * kN * kN;
 #pragma unroll
         for (int rr = 0; rr < 4; ++rr)
-            cp_async16_zfill(&sm.st[stage].s0[srow + 16 * rr][spiece], src + (size_t)(srow + 16 * rr) * kN + spiece, true);
+            cp_async16_zfill(&sm.st[stage].s0[(tid + 128 * rr) >> 6][(tid + 128 * rr) & 63][0], src + (size_t)(tid + 128 * rr) * 8, true);
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();
@@ -636,7 +644,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
             uint32_t b0, b1, b2, b3;
-            ldmatrix_x4_trans(b0, b1, b2, b3, &st.s0[16 * ks + (mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
+            ldmatrix_x4_trans(b0, b1, b2, b3, &st.s0[j0 / 8 + (mi >> 1)][16 * ks + (mi & 1) * 8 + r8][0]);
             mma_bf16(dR0[0], fdy[ks].f[0], fdy[ks].f[1], fdy[ks].f[2], fdy[ks].f[3], b0, b1);
             mma_bf16(dR0[1], fdy[ks].f[0], fdy[ks].f[1], fdy[ks].f[2], fdy[ks].f[3], b2, b3);
             ldmatrix_x4_trans(b0, b1, b2, b3, &sm.ds[16 * ks + (mi & 1) * 8 + r8][j0 + (mi >> 1) * 8]);
@@ -658,8 +666,8 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         {
 #pragma unroll
             for (int ni = 0; ni < 8; ++ni) {
-                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.s0[j0 + g][8 * ni + 2 * q]));
-                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.s0[j0 + g + 8][8 * ni + 2 * q]));
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.s0[ni][j0 + g][2 * q]));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.s0[ni][j0 + g + 8][2 * q]));
                 float p0 = acc[ni][0] * lo.x + acc[ni][2] * hi.x, p1 = acc[ni][1] * lo.y + acc[ni][3] * hi.y;
 #pragma unroll
                 for (int m = 4; m < 32; m <<= 1) {
@@ -687,7 +695,7 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
         }
         __syncthreads();                                              // S4: nobody reads the operand tiles any more
         // ---- epilogue: rows t = g, g + 8; column pairs i = j0 + 8 nt + 2 q, + 1
-        float (*ea)[EPITCH] = reinterpret_cast<float (*)[EPITCH]>(sm.st[stage].s0);
+        float (*ea)[EPITCH] = reinterpret_cast<float (*)[EPITCH]>(&sm.st[stage].s0[0][0][0]);
         float (*eb)[EPITCH] = ea + kC6;
         {
 #pragma unroll
