@@ -30,7 +30,8 @@ namespace {
 constexpr int PITCH = 72;                       // bf16 per shared-memory row (144 bytes): ldmatrix and 4-byte reads hit 32 different banks
 constexpr int kStages = 3;
 struct CarryStage {
-    __nv_bfloat16 m[kC][PITCH];                 // M'[j][j']
+    __nv_bfloat16 m[8][kC][8];                  // M'[j][j'] as it lies in the residual: 8 column blocks of [64 rows j][8 columns j']
+                                                // (a linear copy; the eight rows of an ldmatrix tile are 128 contiguous bytes)
     __nv_bfloat16 rb[kC][PITCH];                // R-[t][j]
     __nv_bfloat16 dy[kC][PITCH];                // dY[t][i]
     float lam[kN];                              // L_C[j]
@@ -87,7 +88,7 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
             const size_t slot = (size_t)bh * nBlk + blk;
             for (int c = tid; c < 512; c += 128) {
                 const int rr = c >> 3, c8 = (c & 7) * 8;
-                cp_async16(&s.m[rr][c8], mprime + slot * (kN * kN) + (size_t)(c & 7) * (kC * 8) + rr * 8);   // 8 column blocks of [64 rows][8]
+                cp_async16(&s.m[c >> 6][c & 63][0], mprime + slot * (kN * kN) + (size_t)c * 8);
                 cp_async16(&s.rb[rr][c8], rbar + seq_base + (size_t)(blk * kC + rr) * tok_stride + c8);
                 if (dy != nullptr) cp_async16(&s.dy[rr][c8], dy + seq_base + (size_t)(blk * kC + rr) * tok_stride + c8);
             }
@@ -152,7 +153,7 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
                 uint32_t b0, b1, b2, b3;    // (tile 2 np: b0, b2), (tile 2 np + 1: b1, b3)
-                ldmatrix_x4(b0, b1, b2, b3, &s.m[np * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)][ks * 16 + (lane >> 4) * 8]);
+                ldmatrix_x4(b0, b1, b2, b3, &s.m[ks * 2 + (lane >> 4)][np * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)][0]);
                 mma_bf16(acc[2 * np], afrag[ks][0], afrag[ks][1], afrag[ks][2], afrag[ks][3], b0, b2);
                 mma_bf16(acc[2 * np + 1], afrag[ks][0], afrag[ks][1], afrag[ks][2], afrag[ks][3], b1, b3);
             }
