@@ -32,6 +32,7 @@ namespace {
 
 typedef __nv_bfloat16 bf;
 constexpr int kC6 = 16;          // tokens per chunk
+constexpr int kRunLen6 = 16;    // chunks per run of the run-parallel backward
 constexpr int PITCH = 72;        // bf16 per shared-memory row (144 bytes): 4-byte fragment reads and ldmatrix rows hit 32 banks
 constexpr int kStages6 = 3;
 constexpr float kMaxHalfDecay = 80.f;   // |sum of lw over half a chunk| the scaling can represent
@@ -795,19 +796,25 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
 // chunk] + dY^T R0 per chunk (and the cotangent of the returned state where it enters), with dS^T in accumulator
 // registers.  It leaves the state gradient at the end of every run of `run_len` chunks, from which the gradient kernel
 // above walks the runs in parallel.
+// Unlike the other kernels of this file it walks 64 tokens at a time: it uses no factor other than exp(cumulative
+// log-decay) <= 1, so nothing limits its chunk, and a quarter of the steps means a quarter of the barriers and waits.
+constexpr int kCB = 64;            // tokens per step of the carry
+constexpr int kCarryStages = 2;
+constexpr int kQT = kCB / 4;       // tokens per thread in phase A
+static_assert(kRunLen6 % (kCB / kC6) == 0, "runs must end at a step of the carry");
 struct CarryStage6 {
-    bf r[kC6][PITCH], w[kC6][PITCH], dy[kC6][PITCH];
+    bf r[kCB][PITCH], w[kCB][PITCH], dy[kCB][PITCH];   // r becomes R0 in place
 };
 struct Carry6Smem {
-    CarryStage6 st[kStages6];
-    bf r0[kC6][PITCH];
-    float tot[2][kN];
+    CarryStage6 st[kCarryStages];
+    float tot[4][kN];              // sum of the log-decay over each quarter of the step
     float wc[kN];
-    unsigned startmask;
-    uint8_t ns[kStages6][kC6];
+    unsigned startmask[2];         // bit t of word t / 32: start flag on token t of the step (one word used when kCB == 32)
+    uint8_t ns[kCarryStages][kCB];
 };
+static_assert(4 * (sizeof(Carry6Smem) + 1024) <= 228 * 1024, "four CTAs per SM");
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 wkv6_carry_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __restrict__ w, int w_per_token,
                       const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts, const bf* __restrict__ dy,
                       const bf* __restrict__ ds_out, const int* __restrict__ residual_mark, int n_runs, int run_len,
@@ -823,56 +830,74 @@ wkv6_carry_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     const size_t seq_base = (size_t)bi * Tlen * tok_stride + (size_t)h * kN;
     const size_t st_base = (size_t)bh * kN * kN;
     const int L = min((int)length[bi], Tlen);
-    const int nC = (Tlen + kC6 - 1) / kC6;
-    const int c_out = L > 0 ? (L - 1) / kC6 : -1, p_out = L > 0 ? (L - 1) % kC6 : -1;
-    const bool split = L > 0 && L < Tlen && p_out != kC6 - 1;
-    const int c_stop = run_len;        // nothing below the first run's end is needed: run 0 starts from the state left there
+    const int nB = (Tlen + kCB - 1) / kCB;                 // steps of the carry
+    const int run_steps = run_len / (kCB / kC6);           // steps per run of the gradient kernel
+    const int c_out = L > 0 ? (L - 1) / kCB : -1, p_out = L > 0 ? (L - 1) % kCB : -1;
+    const bool split = L > 0 && L < Tlen && p_out != kCB - 1;
+    const int c_stop = run_steps;      // nothing below the first run's end is needed: run 0 starts from the state left there
 
     float acc[8][4];
 #pragma unroll
     for (int ni = 0; ni < 8; ++ni)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[ni][e] = 0.f;
-    const int srow = tid >> 3, spiece = (tid & 7) * 8;
     auto issue = [&](int c) {
         if (c >= c_stop) {
-            CarryStage6& st = sm.st[c % kStages6];
-            const int t = c * kC6 + srow;
-            const bool ok = t < Tlen;
-            const size_t off = seq_base + (size_t)(ok ? t : 0) * tok_stride + spiece;
-            cp_async16_zfill(&st.r[srow][spiece], r + off, ok);
-            if (w_per_token) cp_async16_zfill(&st.w[srow][spiece], w + off, ok);
-            cp_async16_zfill(&st.dy[srow][spiece], dy != nullptr ? dy + off : r + off, ok && dy != nullptr);
+            CarryStage6& st = sm.st[c % kCarryStages];
+#pragma unroll
+            for (int rr = 0; rr < kCB / 16; ++rr) {
+                const int row = (tid >> 3) + 16 * rr, piece = (tid & 7) * 8;
+                const int t = c * kCB + row;
+                const bool ok = t < Tlen;
+                const size_t off = seq_base + (size_t)(ok ? t : 0) * tok_stride + piece;
+                cp_async16_zfill(&st.r[row][piece], r + off, ok);
+                if (w_per_token) cp_async16_zfill(&st.w[row][piece], w + off, ok);
+                cp_async16_zfill(&st.dy[row][piece], dy != nullptr ? dy + off : r + off, ok && dy != nullptr);
+            }
         }
         cp_async_commit();
     };
     auto load_ns = [&](int c) -> uint8_t {
-        const int t = c * kC6 + tid;
-        return (tid < kC6 && c >= 0 && t < Tlen) ? new_starts[(size_t)bi * Tlen + t] : (uint8_t)0;
+        const int t = c * kCB + tid;
+        return (tid < kCB && c >= 0 && t < Tlen) ? new_starts[(size_t)bi * Tlen + t] : (uint8_t)0;
     };
-    issue(nC - 1);
-    issue(nC - 2);
-    if (tid < kC6) {
-        sm.ns[(nC - 1) % kStages6][tid] = load_ns(nC - 1);
-        if (nC >= 2) sm.ns[(nC - 2) % kStages6][tid] = load_ns(nC - 2);
+#pragma unroll
+    for (int i = 1; i < kCarryStages; ++i) {
+        issue(nB - i);
+        if (tid < kCB && nB - i >= 0) sm.ns[(nB - i) % kCarryStages][tid] = load_ns(nB - i);
     }
-    uint8_t ns_ahead = load_ns(nC - 3);
-    const int ch = tid & 63, half = tid >> 6;
-    const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
+    uint8_t ns_ahead = load_ns(nB - kCarryStages);
+    // phase A ownership: the channel pair cp, cp + 1 and the kQT tokens of quarter qt
+    const int cp = (tid & 31) * 2, qt = tid >> 5;
+    float2 lw_const = make_float2(0.f, 0.f);
+    if (!w_per_token) {
+        const float2 wv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + (size_t)h * kN + cp));
+        lw_const = make_float2(__logf(wv.x), __logf(wv.y));
+    }
 
     auto walk = [&](auto split_tag, const int c, const int part_arg) {
         constexpr bool kSplitHere = decltype(split_tag)::value;
         const int part = kSplitHere ? part_arg : 0;
-        const int lo = (kSplitHere && part == 1) ? p_out + 1 : 0, hi = (kSplitHere && part == 0) ? p_out + 1 : kC6;
-        const CarryStage6& st = sm.st[c % kStages6];
-        const int t0 = c * kC6;
+        const int lo = (kSplitHere && part == 1) ? p_out + 1 : 0, hi = (kSplitHere && part == 0) ? p_out + 1 : kCB;
+        CarryStage6& st = sm.st[c % kCarryStages];
+        const int t0 = c * kCB;
         if (!kSplitHere || part == 1) {
-            cp_async_wait<1>();
-            __syncthreads();
-            issue(c - 2);
-            if (tid < kC6 && c - 2 >= 0) sm.ns[(c - 2) % kStages6][tid] = ns_ahead;
-            ns_ahead = load_ns(c - 3);
+            cp_async_wait<kCarryStages - 2>();
+            __syncthreads();          // step c has landed for everyone; the tiles of step c + 1 are no longer read
+            issue(c - (kCarryStages - 1));
+            if (tid < kCB && c - (kCarryStages - 1) >= 0) sm.ns[(c - (kCarryStages - 1)) % kCarryStages][tid] = ns_ahead;
+            ns_ahead = load_ns(c - kCarryStages);
         } else {
+            // the first visit turned r into R0 in place: fetch the rows again for the part in front of `length`
+            __syncthreads();
+#pragma unroll
+            for (int rr = 0; rr < kCB / 16; ++rr) {
+                const int row = (tid >> 3) + 16 * rr, piece = (tid & 7) * 8;
+                const int t = t0 + row;
+                const bool ok = t < Tlen;
+                *reinterpret_cast<uint4*>(&st.r[row][piece]) =
+                    ok ? *reinterpret_cast<const uint4*>(r + seq_base + (size_t)t * tok_stride + piece) : make_uint4(0, 0, 0, 0);
+            }
             __syncthreads();
         }
         if (c == c_out && part == 0 && ds_out != nullptr) {
@@ -882,60 +907,81 @@ wkv6_carry_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
                 for (int e = 0; e < 4; ++e)
                     acc[ni][e] += __bfloat162float(ds_out[st_base + (size_t)(8 * ni + 2 * q + (e & 1)) * kN + j0 + g + 8 * (e >> 1)]);
         }
-        if (warp == 0) {
-            const unsigned m = __ballot_sync(0xffffffffu, lane < kC6 && sm.ns[c % kStages6][lane] != 0);
-            if (lane == 0) sm.startmask = m;
+        if (warp < kCB / 32) {
+            const unsigned m = __ballot_sync(0xffffffffu, sm.ns[c % kCarryStages][32 * warp + lane] != 0);
+            if (lane == 0) sm.startmask[warp] = m;
         }
-        float lw[8], cl[8];
-        float run = 0.f;
-#pragma unroll
-        for (int tt = 0; tt < 8; ++tt) {
-            const int t = 8 * half + tt;
+        // the log-decay of this thread's kQT tokens (two channels each), and its sum
+        auto lw_of = [&](int tt) -> float2 {
+            const int t = kQT * qt + tt;
             const bool ok = t0 + t < Tlen && t >= lo && t < hi;
-            lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
-            run += lw[tt];
-            cl[tt] = run;
+            return !ok ? make_float2(0.f, 0.f)
+                       : (w_per_token ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.w[t][cp])) : lw_const);
+        };
+        float2 run = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int tt = 0; tt < kQT; ++tt) {
+            const float2 l2 = lw_of(tt);
+            run.x += l2.x;
+            run.y += l2.y;
         }
-        sm.tot[half][ch] = run;
+        *reinterpret_cast<float2*>(&sm.tot[qt][cp]) = run;
         __syncthreads();
         {
-            const unsigned starts = sm.startmask;
-            auto seg_of = [&](int t) { return __popc(starts & ((2u << t) - 1u)); };
+            const unsigned long long starts = (unsigned long long)sm.startmask[0] | (kCB > 32 ? (unsigned long long)sm.startmask[1] << 32 : 0ull);
+            auto seg_of = [&](int t) { return __popcll(starts & ((2ull << t) - 1ull)); };
             const int seg_last = seg_of(hi - 1), seg_base = lo > 0 ? seg_of(lo - 1) : 0;
-            const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
-            const float base = half ? c_m : 0.f;
-            if (half) sm.wc[ch] = seg_last == seg_base ? __expf(c_C) : 0.f;
+            float2 c_prev = make_float2(0.f, 0.f);         // cumulative log-decay in front of the token
+            for (int qq = 0; qq < qt; ++qq) {
+                const float2 tq = *reinterpret_cast<const float2*>(&sm.tot[qq][cp]);
+                c_prev.x += tq.x;
+                c_prev.y += tq.y;
+            }
+            if (qt == 3)
+                *reinterpret_cast<float2*>(&sm.wc[cp]) = seg_last == seg_base ? make_float2(__expf(c_prev.x + run.x), __expf(c_prev.y + run.y))
+                                                                               : make_float2(0.f, 0.f);
+            int seg = qt > 0 ? seg_of(kQT * qt - 1) : 0;    // number of start flags at or before the token, kept in step
 #pragma unroll
-            for (int tt = 0; tt < 8; ++tt) {
-                const int t = 8 * half + tt;
+            for (int tt = 0; tt < kQT; ++tt) {
+                const int t = kQT * qt + tt;
+                seg += (int)((starts >> t) & 1ull);
                 const bool in_part = t >= lo && t < hi;
-                const float c_prev = base + cl[tt] - lw[tt];
-                const float rv = in_part ? __bfloat162float(st.r[t][ch]) : 0.f;
-                sm.r0[t][ch] = __float2bfloat16_rn(seg_of(t) == seg_base ? rv * __expf(c_prev) : 0.f);
+                const float2 rv = in_part ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.r[t][cp])) : make_float2(0.f, 0.f);
+                const bool first_seg = seg == seg_base;
+                *reinterpret_cast<uint32_t*>(&st.r[t][cp]) =                                   // R0, in place
+                    pack2(first_seg ? rv.x * __expf(c_prev.x) : 0.f, first_seg ? rv.y * __expf(c_prev.y) : 0.f);
+                const float2 l2 = lw_of(tt);
+                c_prev.x += l2.x;
+                c_prev.y += l2.y;
             }
         }
         __syncthreads();
-        {
+        // dS0^T = dS_C^T diag(exp(c_C)) [no start in the step] + dY^T R0
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            const float2 w0 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 2 * q]);
+            const float2 w1 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 8 + 2 * q]);
+            acc[2 * np][0] *= w0.x; acc[2 * np][1] *= w0.y; acc[2 * np][2] *= w0.x; acc[2 * np][3] *= w0.y;
+            acc[2 * np + 1][0] *= w1.x; acc[2 * np + 1][1] *= w1.y; acc[2 * np + 1][2] *= w1.x; acc[2 * np + 1][3] *= w1.y;
+        }
+#pragma unroll
+        for (int ks = 0; ks < kCB / 16; ++ks) {
             uint32_t ya[4];
-            ldmatrix_x4_trans(ya[0], ya[1], ya[2], ya[3], &st.dy[(mi >> 1) * 8 + r8][j0 + (mi & 1) * 8]);
+            ldmatrix_x4_trans(ya[0], ya[1], ya[2], ya[3], &st.dy[16 * ks + (mi >> 1) * 8 + r8][j0 + (mi & 1) * 8]);
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
-                const float2 w0 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 2 * q]);
-                const float2 w1 = *reinterpret_cast<const float2*>(&sm.wc[16 * np + 8 + 2 * q]);
-                acc[2 * np][0] *= w0.x; acc[2 * np][1] *= w0.y; acc[2 * np][2] *= w0.x; acc[2 * np][3] *= w0.y;
-                acc[2 * np + 1][0] *= w1.x; acc[2 * np + 1][1] *= w1.y; acc[2 * np + 1][2] *= w1.x; acc[2 * np + 1][3] *= w1.y;
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(b0, b1, b2, b3, &sm.r0[(mi & 1) * 8 + r8][(2 * np + (mi >> 1)) * 8]);
+                ldmatrix_x4_trans(b0, b1, b2, b3, &st.r[16 * ks + (mi & 1) * 8 + r8][(2 * np + (mi >> 1)) * 8]);
                 mma_bf16(acc[2 * np], ya[0], ya[1], ya[2], ya[3], b0, b1);
                 mma_bf16(acc[2 * np + 1], ya[0], ya[1], ya[2], ya[3], b2, b3);
             }
         }
     };
-    for (int c = nC - 1; c >= c_stop - 1; --c) {
-        // the state gradient behind the last chunk of a run (before anything of that chunk is applied), for the CTA of
+    for (int c = nB - 1; c >= c_stop - 1; --c) {
+        // the state gradient behind the last step of a run (before anything of that step is applied), for the CTA of
         // the gradient kernel that walks the run
-        if ((c + 1) % run_len == 0 && c + 1 < nC) {
-            bf* dst = dsck + ((size_t)bh * n_runs + c / run_len) * kN * kN;
+        if ((c + 1) % run_steps == 0 && c + 1 < nB) {
+            bf* dst = dsck + ((size_t)bh * n_runs + c / run_steps) * kN * kN;
 #pragma unroll
             for (int ni = 0; ni < 8; ++ni) {
                 *reinterpret_cast<uint32_t*>(dst + (size_t)(j0 + g) * kN + 8 * ni + 2 * q) = pack2(acc[ni][0], acc[ni][1]);
@@ -972,7 +1018,7 @@ __global__ void wkv6_reduce_runs_kernel(int BH, int n_runs, const float* __restr
 }  // namespace
 
 // How the backward cuts a sequence: runs of 16 chunks (256 tokens) once there are at least two of them.
-constexpr int kRunLen = 16;
+constexpr int kRunLen = kRunLen6;
 static int runs_of(int T) {
     const int nC = (T + kC6 - 1) / kC6;
     return nC >= 2 * kRunLen ? (nC + kRunLen - 1) / kRunLen : 1;

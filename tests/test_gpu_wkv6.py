@@ -230,3 +230,16 @@ def test_chunked_forward_without_residual_matches_oracle():
     assert rel_err(npf(y), yo) < TOL[torch.bfloat16]
     for i in range(3):
         assert rel_err(npf(s[i]), so[i]) < TOL[torch.bfloat16]
+
+
+def test_run_parallel_backward_ragged():
+    """From 32 chunks on, the backward is a state-gradient carry (64 tokens per step) plus the gradient kernel over runs of
+    16 chunks.  T = 560 is 35 chunks, three runs and nine carry steps of which the last has 48 tokens; the lengths put
+    the cotangent of the returned state on a step boundary, on a run boundary, one token short of each, inside a step and
+    at 1, and start flags lie on, next to and far from those positions."""
+    T = 560
+    starts = [[0, 64, 65, 300, 511, 512, 559], [256, 257, 558], [513], [100, 511], [0, 299, 300, 301], [0]]
+    lengths = [T, T - 1, 513, 512, 300, 1]
+    d = case("6", 6, T, 2, seed=977, starts=starts, lengths=lengths, s0_scale=0.5)
+    assert _fwd_mark("6", d) == 0
+    check("6", d, torch.bfloat16)
