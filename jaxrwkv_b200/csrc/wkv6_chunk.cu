@@ -104,12 +104,26 @@ __device__ __forceinline__ float warp_sum8(const float* v, int lane, int* which)
     return c;
 }
 
+// The same for four values with six shuffles: which = 2 bit4(lane) + bit3(lane); every lane ends with the total.
+__device__ __forceinline__ float warp_sum4(const float* v, int lane, int* which) {
+    const bool b4 = lane & 16, b3 = lane & 8;
+    float a[2], c;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) a[j] = (b4 ? v[j + 2] : v[j]) + __shfl_xor_sync(0xffffffffu, b4 ? v[j] : v[j + 2], 16);
+    c = (b3 ? a[1] : a[0]) + __shfl_xor_sync(0xffffffffu, b3 ? a[0] : a[1], 8);
+    c += __shfl_xor_sync(0xffffffffu, c, 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    *which = (b4 ? 2 : 0) + (b3 ? 1 : 0);
+    return c;
+}
+
 // ------------------------------------------------------------------ forward ---------
 struct Fwd6cSmem {
     RawStage raw[kStages6];
     bf rt[kC6][PITCH], kt[kC6][PITCH], r0[kC6][PITCH], kh[kC6][PITCH];   // R~, K~, R0, K^
     bf ys[kC6][PITCH];                                                   // the chunk's outputs, token-major
-    float tot[2][kN];        // sum of lw over each half of the chunk
+    float tot[4][kN];        // sum of lw over each quarter of the chunk
     float wc[kN];            // exp(c_C), or 0 when a start flag lies in the chunk
     float dpart[2][kC6];     // sum_i r u k per token, one partial per 32 channels
     int seg[kC6];            // number of start flags at or before the token, inside the chunk
@@ -186,10 +200,15 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     }
     uint8_t ns_ahead = load_ns(2);
 
-    // phase A ownership: channel ch, tokens 8 half .. 8 half + 7
-    const int ch = tid & 63, half = tid >> 6;
-    const float uu = __bfloat162float(u[(size_t)h * kN + ch]);
-    const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
+    // phase A ownership: the channel pair cp, cp + 1 and the four tokens of quarter qt (= the warp, which so holds all 64
+    // channels of its tokens)
+    const int cp = (tid & 31) * 2, qt = warp;
+    const float2 uu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(u + (size_t)h * kN + cp));
+    float2 lw_const = make_float2(0.f, 0.f);
+    if (!w_per_token) {
+        const float2 wv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + (size_t)h * kN + cp));
+        lw_const = make_float2(__logf(wv.x), __logf(wv.y));
+    }
     bool bad = false;
 
     // One chunk, or one part of the split chunk.  The two cases are separate instantiations: in the common one the
@@ -228,50 +247,61 @@ wkv6_chunk_fwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             const unsigned m = __ballot_sync(0xffffffffu, lane < kC6 && sm.ns[c % kStages6][lane] != 0);
             if (lane == 0) sm.startmask = m;
         }
-        float lw[8], cl[8];
-        float run = 0.f;
+        float2 lw[4], cl[4];
+        float2 run = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int tt = 0; tt < 8; ++tt) {
-            const int t = 8 * half + tt;
+        for (int tt = 0; tt < 4; ++tt) {
+            const int t = 4 * qt + tt;
             const bool ok = t0 + t < Tlen && t >= lo && t < hi;
-            lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
-            if (!(lw[tt] <= 0.f)) bad = true;      // a decay above 1 (or NaN) is outside what the scaling covers
-            run += lw[tt];
+            lw[tt] = !ok ? make_float2(0.f, 0.f)
+                         : (w_per_token ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.w[t][cp])) : lw_const);
+            if (!(lw[tt].x <= 0.f) || !(lw[tt].y <= 0.f)) bad = true;      // a decay above 1 (or NaN) is outside what the scaling covers
+            run.x += lw[tt].x;
+            run.y += lw[tt].y;
             cl[tt] = run;
         }
-        sm.tot[half][ch] = run;
-        // the operands need the other half's total: a barrier of the whole CTA
+        *reinterpret_cast<float2*>(&sm.tot[qt][cp]) = run;
+        // the operands need the other quarters' totals: a barrier of the whole CTA
         __syncthreads();
         // segments: seg(t) = number of start flags at or before token t
         const unsigned starts = sm.startmask;
         auto seg_of = [&](int t) { return __popc(starts & ((2u << t) - 1u)); };
         const int seg_last = seg_of(hi - 1), seg_base = lo > 0 ? seg_of(lo - 1) : 0;   // of the part's last token; of the state entering it
-        int seg_mine[8];
-#pragma unroll
-        for (int tt = 0; tt < 8; ++tt) seg_mine[tt] = seg_of(8 * half + tt);
         if (tid < kC6) sm.seg[tid] = seg_of(tid);
-        const float tot0 = sm.tot[0][ch], tot1 = sm.tot[1][ch];
-        if (fabsf(tot0) > kMaxHalfDecay || fabsf(tot1) > kMaxHalfDecay) bad = true;
-        const float c_m = fmaxf(tot0, -kMaxHalfDecay), c_C = c_m + fmaxf(tot1, -kMaxHalfDecay);
-        const float base = half ? c_m : 0.f;
-        if (half) sm.wc[ch] = seg_last == seg_base ? __expf(c_C) : 0.f;
-        float dsum[8];
+        const float2 tq0 = *reinterpret_cast<const float2*>(&sm.tot[0][cp]), tq1 = *reinterpret_cast<const float2*>(&sm.tot[1][cp]);
+        const float2 tq2 = *reinterpret_cast<const float2*>(&sm.tot[2][cp]), tq3 = *reinterpret_cast<const float2*>(&sm.tot[3][cp]);
+        const float2 tot0 = make_float2(tq0.x + tq1.x, tq0.y + tq1.y), tot1 = make_float2(tq2.x + tq3.x, tq2.y + tq3.y);
+        if (fabsf(tot0.x) > kMaxHalfDecay || fabsf(tot1.x) > kMaxHalfDecay || fabsf(tot0.y) > kMaxHalfDecay || fabsf(tot1.y) > kMaxHalfDecay) bad = true;
+        const float2 c_m = make_float2(fmaxf(tot0.x, -kMaxHalfDecay), fmaxf(tot0.y, -kMaxHalfDecay));
+        const float2 c_C = make_float2(c_m.x + fmaxf(tot1.x, -kMaxHalfDecay), c_m.y + fmaxf(tot1.y, -kMaxHalfDecay));
+        // cumulative log-decay in front of this quarter (the second half counts from the clamped middle, as c_C does)
+        const float2 base = qt == 0 ? make_float2(0.f, 0.f) : (qt == 1 ? tq0 : (qt == 2 ? c_m : make_float2(c_m.x + tq2.x, c_m.y + tq2.y)));
+        if (qt == 3)
+            *reinterpret_cast<float2*>(&sm.wc[cp]) = seg_last == seg_base ? make_float2(__expf(c_C.x), __expf(c_C.y)) : make_float2(0.f, 0.f);
+        float dsum[4];
 #pragma unroll
-        for (int tt = 0; tt < 8; ++tt) {
-            const int t = 8 * half + tt;
+        for (int tt = 0; tt < 4; ++tt) {
+            const int t = 4 * qt + tt;
             const bool in_part = t >= lo && t < hi;
-            const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
-            const float rv = in_part ? __bfloat162float(st.r[t][ch]) : 0.f, kv = in_part ? __bfloat162float(st.k[t][ch]) : 0.f;
-            sm.rt[t][ch] = __float2bfloat16_rn(rv * __expf(fminf(c_prev - c_m, kMaxHalfDecay)));
-            sm.kt[t][ch] = __float2bfloat16_rn(kv * __expf(fminf(c_m - c_t, kMaxHalfDecay)));
-            sm.r0[t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_base ? rv * __expf(c_prev) : 0.f);
-            sm.kh[t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
-            dsum[tt] = rv * uu * kv;
+            const int seg_t = seg_of(t);
+            const float2 c_t = make_float2(base.x + cl[tt].x, base.y + cl[tt].y), c_prev = make_float2(c_t.x - lw[tt].x, c_t.y - lw[tt].y);
+            const float2 zero2 = make_float2(0.f, 0.f);
+            const float2 rv = in_part ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.r[t][cp])) : zero2;
+            const float2 kv = in_part ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.k[t][cp])) : zero2;
+            *reinterpret_cast<uint32_t*>(&sm.rt[t][cp]) = pack2(rv.x * __expf(fminf(c_prev.x - c_m.x, kMaxHalfDecay)), rv.y * __expf(fminf(c_prev.y - c_m.y, kMaxHalfDecay)));
+            *reinterpret_cast<uint32_t*>(&sm.kt[t][cp]) = pack2(kv.x * __expf(fminf(c_m.x - c_t.x, kMaxHalfDecay)), kv.y * __expf(fminf(c_m.y - c_t.y, kMaxHalfDecay)));
+            const bool first = seg_t == seg_base, last = seg_t == seg_last;
+            *reinterpret_cast<uint32_t*>(&sm.r0[t][cp]) = pack2(first ? rv.x * __expf(c_prev.x) : 0.f, first ? rv.y * __expf(c_prev.y) : 0.f);
+            *reinterpret_cast<uint32_t*>(&sm.kh[t][cp]) = pack2(last ? kv.x * __expf(c_C.x - c_t.x) : 0.f, last ? kv.y * __expf(c_C.y - c_t.y) : 0.f);
+            dsum[tt] = fmaf(rv.x * uu.x, kv.x, rv.y * uu.y * kv.y);
         }
         {
             int which;
-            const float total = warp_sum8(dsum, lane, &which);
-            if (q == 0) sm.dpart[warp & 1][8 * half + which] = total;
+            const float total = warp_sum4(dsum, lane, &which);      // over all 64 channels: the warp holds them all
+            if ((lane & 7) == 0) {
+                sm.dpart[0][4 * qt + which] = total;
+                sm.dpart[1][4 * qt + which] = 0.f;
+            }
         }
         __syncthreads();
 
