@@ -407,7 +407,7 @@ struct Bwd6cSmem {
     bf ds[kN][PITCH];          // dS_C^T[j][i] in bf16, for the one product that contracts over j
     float e2[kC6][EPITCH], e3[kC6][EPITCH];   // exp(c_{t-1} - c_m) and exp(c_m - c_t): what turns dR~, dK~ into dr, dk
     float em[kN], ecm[kN];     // exp(c_m) and exp(c_C - c_m): the same for dR0 and dK^
-    float tot[2][kN];
+    float tot[4][kN];          // sum of lw over each quarter of the chunk
     float wc[kN];              // exp(c_C), or 0 when a start flag lies in the chunk
     float lump[kN];            // what every token of the chunk receives: the K^ references and the carried state
     float gw[4][kN];           // sum_j dS_C S0 over each warp's value rows
@@ -507,9 +507,14 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
     if (tid < kC6) sm.ns[0][tid] = load_ns(c_hi - 1);
     uint8_t ns_ahead = load_ns(c_hi - 2);
 
-    const int ch = tid & 63, half = tid >> 6;
-    const float uu_a = __bfloat162float(u[(size_t)h * kN + ch]);
-    const float lw_const = w_per_token ? 0.f : __logf(__bfloat162float(w[(size_t)h * kN + ch]));
+    // phase A ownership as in the forward: the channel pair cp, cp + 1 and the four tokens of quarter qt (= the warp)
+    const int cp = (tid & 31) * 2, qt = warp;
+    const float2 uu_a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(u + (size_t)h * kN + cp));
+    float2 lw_const = make_float2(0.f, 0.f);
+    if (!w_per_token) {
+        const float2 wv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + (size_t)h * kN + cp));
+        lw_const = make_float2(__logf(wv.x), __logf(wv.y));
+    }
     float u_col[2][2];                         // u of this thread's four result columns
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
@@ -561,52 +566,63 @@ wkv6_chunk_bwd_kernel(int Tlen, int H, const bf* __restrict__ r, const bf* __res
             const unsigned m = __ballot_sync(0xffffffffu, lane < kC6 && sm.ns[stage][lane] != 0);
             if (lane == 0) sm.startmask = m;
         }
-        float lw[8], cl[8];
-        float run = 0.f;
+        float2 lw[4], cl[4];
+        float2 run = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int tt = 0; tt < 8; ++tt) {
-            const int t = 8 * half + tt;
+        for (int tt = 0; tt < 4; ++tt) {
+            const int t = 4 * qt + tt;
             const bool ok = t0 + t < Tlen && t >= lo && t < hi;
-            lw[tt] = !ok ? 0.f : (w_per_token ? __bfloat162float(st.w[t][ch]) : lw_const);
-            run += lw[tt];
+            lw[tt] = !ok ? make_float2(0.f, 0.f)
+                         : (w_per_token ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.w[t][cp])) : lw_const);
+            run.x += lw[tt].x;
+            run.y += lw[tt].y;
             cl[tt] = run;
         }
-        sm.tot[half][ch] = run;
+        *reinterpret_cast<float2*>(&sm.tot[qt][cp]) = run;
         __syncthreads();                                              // S2
         {
             const unsigned starts = sm.startmask;
             auto seg_of = [&](int t) { return __popc(starts & ((2u << t) - 1u)); };
             const int seg_last = seg_of(hi - 1), seg_base = lo > 0 ? seg_of(lo - 1) : 0;
-            int seg_mine[8];
-#pragma unroll
-            for (int tt = 0; tt < 8; ++tt) seg_mine[tt] = seg_of(8 * half + tt);
             if (tid < kC6) sm.seg[tid] = seg_of(tid);
-            const float c_m = fmaxf(sm.tot[0][ch], -kMaxHalfDecay), c_C = c_m + fmaxf(sm.tot[1][ch], -kMaxHalfDecay);
-            const float base = half ? c_m : 0.f;
-            if (half) {
-                sm.wc[ch] = seg_last == seg_base ? __expf(c_C) : 0.f;
-                sm.em[ch] = __expf(c_m);
-                sm.ecm[ch] = __expf(c_C - c_m);
+            const float2 tq0 = *reinterpret_cast<const float2*>(&sm.tot[0][cp]), tq1 = *reinterpret_cast<const float2*>(&sm.tot[1][cp]);
+            const float2 tq2 = *reinterpret_cast<const float2*>(&sm.tot[2][cp]), tq3 = *reinterpret_cast<const float2*>(&sm.tot[3][cp]);
+            const float2 c_m = make_float2(fmaxf(tq0.x + tq1.x, -kMaxHalfDecay), fmaxf(tq0.y + tq1.y, -kMaxHalfDecay));
+            const float2 c_C = make_float2(c_m.x + fmaxf(tq2.x + tq3.x, -kMaxHalfDecay), c_m.y + fmaxf(tq2.y + tq3.y, -kMaxHalfDecay));
+            const float2 base = qt == 0 ? make_float2(0.f, 0.f) : (qt == 1 ? tq0 : (qt == 2 ? c_m : make_float2(c_m.x + tq2.x, c_m.y + tq2.y)));
+            if (qt == 3) {
+                const bool carried = seg_last == seg_base;
+                *reinterpret_cast<float2*>(&sm.wc[cp]) = carried ? make_float2(__expf(c_C.x), __expf(c_C.y)) : make_float2(0.f, 0.f);
+                *reinterpret_cast<float2*>(&sm.em[cp]) = make_float2(__expf(c_m.x), __expf(c_m.y));
+                *reinterpret_cast<float2*>(&sm.ecm[cp]) = make_float2(__expf(c_C.x - c_m.x), __expf(c_C.y - c_m.y));
             }
-            float dsum[8];
+            float dsum[4];
 #pragma unroll
-            for (int tt = 0; tt < 8; ++tt) {
-                const int t = 8 * half + tt;
-                const float c_t = base + cl[tt], c_prev = c_t - lw[tt];
+            for (int tt = 0; tt < 4; ++tt) {
+                const int t = 4 * qt + tt;
+                const int seg_t = seg_of(t);
+                const float2 c_t = make_float2(base.x + cl[tt].x, base.y + cl[tt].y), c_prev = make_float2(c_t.x - lw[tt].x, c_t.y - lw[tt].y);
                 const bool in_part = t >= lo && t < hi;
-                const float rv = in_part ? __bfloat162float(st.r[t][ch]) : 0.f, kv = in_part ? __bfloat162float(st.k[t][ch]) : 0.f;
-                const float f2 = __expf(fminf(c_prev - c_m, kMaxHalfDecay)), f3 = __expf(fminf(c_m - c_t, kMaxHalfDecay));
-                sm.e2[t][ch] = f2;
-                sm.e3[t][ch] = f3;
-                sm.ops[0][t][ch] = __float2bfloat16_rn(rv * f2);
-                sm.ops[1][t][ch] = __float2bfloat16_rn(kv * f3);
-                sm.ops[2][t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_base ? rv * __expf(c_prev) : 0.f);
-                sm.ops[3][t][ch] = __float2bfloat16_rn(seg_mine[tt] == seg_last ? kv * __expf(c_C - c_t) : 0.f);
-                dsum[tt] = rv * uu_a * kv;
+                const float2 zero2 = make_float2(0.f, 0.f);
+                const float2 rv = in_part ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.r[t][cp])) : zero2;
+                const float2 kv = in_part ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&st.k[t][cp])) : zero2;
+                const float2 f2 = make_float2(__expf(fminf(c_prev.x - c_m.x, kMaxHalfDecay)), __expf(fminf(c_prev.y - c_m.y, kMaxHalfDecay)));
+                const float2 f3 = make_float2(__expf(fminf(c_m.x - c_t.x, kMaxHalfDecay)), __expf(fminf(c_m.y - c_t.y, kMaxHalfDecay)));
+                *reinterpret_cast<float2*>(&sm.e2[t][cp]) = f2;
+                *reinterpret_cast<float2*>(&sm.e3[t][cp]) = f3;
+                const bool first = seg_t == seg_base, last = seg_t == seg_last;
+                *reinterpret_cast<uint32_t*>(&sm.ops[0][t][cp]) = pack2(rv.x * f2.x, rv.y * f2.y);
+                *reinterpret_cast<uint32_t*>(&sm.ops[1][t][cp]) = pack2(kv.x * f3.x, kv.y * f3.y);
+                *reinterpret_cast<uint32_t*>(&sm.ops[2][t][cp]) = pack2(first ? rv.x * __expf(c_prev.x) : 0.f, first ? rv.y * __expf(c_prev.y) : 0.f);
+                *reinterpret_cast<uint32_t*>(&sm.ops[3][t][cp]) = pack2(last ? kv.x * __expf(c_C.x - c_t.x) : 0.f, last ? kv.y * __expf(c_C.y - c_t.y) : 0.f);
+                dsum[tt] = fmaf(rv.x * uu_a.x, kv.x, rv.y * uu_a.y * kv.y);
             }
             int which;
-            const float total = warp_sum8(dsum, lane, &which);
-            if (q == 0) sm.dpart[warp & 1][8 * half + which] = total;
+            const float total = warp_sum4(dsum, lane, &which);       // over all 64 channels: the warp holds them all
+            if ((lane & 7) == 0) {
+                sm.dpart[0][4 * qt + which] = total;
+                sm.dpart[1][4 * qt + which] = 0.f;
+            }
         }
         __syncthreads();                                              // S3
         const bf (*Rt)[PITCH] = sm.ops[0];
