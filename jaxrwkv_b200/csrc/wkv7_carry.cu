@@ -10,7 +10,7 @@
 // CTA of four warps walks one sequence from its last block to its first with the state gradient in
 // registers (fp32, each warp 16 rows as mma.sync accumulator tiles): an accumulator tile is already in the
 // register layout of the next product's left operand, so nothing passes through shared memory between
-// blocks.  M', R-, dY and L_C of the blocks ahead arrive by cp.async, three blocks deep.  The gradient
+// blocks.  M', R-, dY and L_C of the blocks ahead arrive by cp.async, two or three blocks deep.  The gradient
 // leaving every block goes to global memory in bf16; the second part (wkv7_grad.cu) turns it, block by
 // block and in parallel over all blocks, into the gradients of the six streams.
 //
@@ -28,7 +28,8 @@ namespace b200wkv {
 namespace {
 
 constexpr int PITCH = 72;                       // bf16 per shared-memory row (144 bytes): ldmatrix and 4-byte reads hit 32 different banks
-constexpr int kStages = 3;
+// Depth of the cp.async ring: three stages (two CTAs per SM) while every sequence has a resident CTA anyway, two stages
+// (four CTAs per SM) when there are more sequences than that, so that more of these latency-bound chains run at once.
 struct CarryStage {
     __nv_bfloat16 m[8][kC][8];                  // M'[j][j'] as it lies in the residual: 8 column blocks of [64 rows j][8 columns j']
                                                 // (a linear copy; the eight rows of an ldmatrix tile are 128 contiguous bytes)
@@ -36,7 +37,8 @@ struct CarryStage {
     __nv_bfloat16 dy[kC][PITCH];                // dY[t][i]
     float lam[kN];                              // L_C[j]
 };
-constexpr int CARRY_SMEM = kStages * (int)sizeof(CarryStage);
+template <int kStages>
+constexpr int carry_smem() { return kStages * (int)sizeof(CarryStage); }
 
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
@@ -62,6 +64,7 @@ __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+template <int kStages>
 __global__ void __launch_bounds__(128)
 wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, const uint8_t* __restrict__ new_starts,
                       const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ ds_out,
@@ -113,13 +116,13 @@ wkv7_carry_bwd_kernel(int Tlen, int H, const uint32_t* __restrict__ length, cons
         }
     };
 
-    issue(nBlk - 1);
-    issue(nBlk - 2);
+#pragma unroll
+    for (int i = 1; i < kStages; ++i) issue(nBlk - i);
     uint8_t flag_here = new_starts[(size_t)bi * Tlen + (size_t)(nBlk - 1) * kC];   // start flag of the block's first token
     for (int blk = nBlk - 1; blk >= 0; --blk) {
-        cp_async_wait<1>();                     // the copies of block blk have landed (one younger group may be in flight)
+        cp_async_wait<kStages - 2>();           // the copies of block blk have landed (younger groups may be in flight)
         __syncthreads();                        // ... for every thread; and everyone is done with the stage refilled next
-        issue(blk - 2);
+        issue(blk - (kStages - 1));
         const uint8_t flag_next = (blk > 0) ? new_starts[(size_t)bi * Tlen + (size_t)(blk - 1) * kC] : 0;   // asked for a block ahead
         const CarryStage& s = stages[blk % kStages];
         const int p1 = (blk + 1) * kC;
@@ -196,13 +199,19 @@ int wkv7_carry_bwd(cudaStream_t st, int B, int T, int H, const uint32_t* length,
                    const void* ds_out, void* residual, const int* residual_mark, void* ds0) {
     typedef __nv_bfloat16 bf;
     static DeviceOnce smem_attr;
-    if (!smem_attr.ok([]() { return cudaFuncSetAttribute(wkv7_carry_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CARRY_SMEM); }))
+    if (!smem_attr.ok([]() {
+            cudaError_t e = cudaFuncSetAttribute(wkv7_carry_bwd_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, carry_smem<3>());
+            if (e != cudaSuccess) return e;
+            return cudaFuncSetAttribute(wkv7_carry_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, carry_smem<2>());
+        }))
         return B200WKV_ELAUNCH;
     const CarryLayout lay = carry_layout(B, T, H);
     char* base = static_cast<char*>(residual);
-    wkv7_carry_bwd_kernel<<<B * H, 128, CARRY_SMEM, st>>>(T, H, length, ns, (const bf*)dy, (const bf*)ds_out, (const bf*)(base + lay.mprime),
-                                                          (const bf*)(base + lay.rbar), (const float*)(base + lay.lam),
-                                                          (const int*)(base + lay.fast), residual_mark, (bf*)(base + lay.dstate), (bf*)ds0);
+    const bool deep = (long long)B * H <= 2LL * sm_count_of_current_device();
+    auto launch = deep ? wkv7_carry_bwd_kernel<3> : wkv7_carry_bwd_kernel<2>;
+    launch<<<B * H, 128, deep ? carry_smem<3>() : carry_smem<2>(), st>>>(T, H, length, ns, (const bf*)dy, (const bf*)ds_out, (const bf*)(base + lay.mprime),
+                                                                         (const bf*)(base + lay.rbar), (const float*)(base + lay.lam),
+                                                                         (const int*)(base + lay.fast), residual_mark, (bf*)(base + lay.dstate), (bf*)ds0);
     return cudaGetLastError() == cudaSuccess ? B200WKV_OK : B200WKV_ELAUNCH;
 }
 

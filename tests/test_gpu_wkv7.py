@@ -433,6 +433,27 @@ def test_bwd_carry_and_gradient_kernels_many_sequences():
             assert rel_err(npf(a), b) < TOL[torch.bfloat16], (n, bi, hh, rel_err(npf(a), b))
 
 
+def test_bwd_carry_ring_depths_agree():
+    """With more sequences than two per SM the state-gradient carry runs a shallower copy ring at four CTAs per SM; the
+    same rows in two calls of half the batch take the deeper ring: every gradient must be bit-identical."""
+    B, T, H = 10, 256, 32
+    starts = [[0], [], [0, 128], [64], [0], [192], [], [0, 64, 128, 192], [], [0]]
+    lengths = [T, T, 128, T, 0, T, 64, T, T + 5, 192]
+    d = wkv7_case(B, T, H, seed=91, s0_scale=0.4, starts=starts, lengths=lengths)
+    t = to_dev(d, torch.bfloat16)
+    length, ns = flags(d)
+    s, y, res = run_fwd(t, length, ns)
+    gy, gs = torch.randn_like(y), torch.randn_like(s)
+    whole = rwkv7.batched_wkv7_bwd(res, (gs, gy), B)
+    for lo in (0, 5):
+        th = {n: v[lo:lo + 5].contiguous() for n, v in t.items()}
+        s_h, y_h, res_h = run_fwd(th, length[lo:lo + 5].contiguous(), ns[lo:lo + 5].contiguous())
+        assert torch.equal(y_h, y[lo:lo + 5]) and torch.equal(s_h, s[lo:lo + 5])
+        half = rwkv7.batched_wkv7_bwd(res_h, (gs[lo:lo + 5].contiguous(), gy[lo:lo + 5].contiguous()), 5)
+        for a, b in zip(half, whole):
+            assert torch.equal(a, b[lo:lo + 5])
+
+
 def test_bwd_headline_shape_against_oracle_slices():
     """The benchmark's own shape and flags (B=8, T=4096, H=32, a start at t=0 only, length = T): the path the
     headline number times.  Four (batch, head) slices of every gradient against the oracle."""
