@@ -50,11 +50,11 @@ METRIC = "wkv7_fwd_bwd_tokens_per_s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch at B=8, T=4096, H=32 from the
 # ncu captures summarised under profiles/, with the hash of the kernel sources they were taken from.
 # Traffic is proportional to B; the figure is dropped (null) when the sources no longer match.
-NCU_TRAFFIC = {"sources": "b34cecfdc36f", "B": 8, "wkv7_fwd": 1973.4e6, "wkv7_bwd": 521.4e6 + 2672.1e6}
+NCU_TRAFFIC = {"sources": "20d31d569af8", "B": 8, "wkv7_fwd": 1974.2e6, "wkv7_bwd": 521.5e6 + 2670.7e6}
 # The backward call is timed as a whole (CUDA events around the call): its device time is the sequential
 # state-gradient carry followed by the block-parallel gradient kernel; the launch list under profiles/
 # gives each kernel's share.  Traffic of the backward is the sum over both kernels.
-KERNELS = {"wkv7_fwd": ["wkv7_chunk_fwd_kernel"], "wkv7_bwd": ["wkv7_carry_bwd_kernel", "wkv7_grad_bwd_kernel"]}
+KERNELS = {"wkv7_fwd": ["wkv7_chunk_fwd_kernel"], "wkv7_bwd": ["wkv7_carry_bwd_kernel<3>", "wkv7_grad_bwd_kernel"]}
 
 
 def kernel_source_hash():
